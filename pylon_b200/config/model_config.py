@@ -478,3 +478,235 @@ class FikeraxConfig:
             order += [(index, turn > 0 and index == self.loop_start) for index in range(self.loop_start, self.loop_stop)]
         order += [(index, False) for index in range(self.loop_stop, len(self.layers))]
         return order
+
+
+# ---------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class ZemavikAttention:
+    """The attending half of a ``parallel`` mixer: grouped-query attention without positions, scores times ``scale``, inside
+    chunks of ``chunk`` positions (``None``: every earlier key), values of their own width."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    chunk: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "ZemavikAttention":
+        heads, kv_heads = _positive_int(data, "heads"), _positive_int(data, "kv_heads")
+        if heads % kv_heads:
+            raise ConfigError(f"{where}: {heads} heads cannot be grouped over {kv_heads} kv_heads")
+        mask = data.get("mask")
+        return cls(heads, kv_heads, _positive_int(data, "dim"), _positive_int(data, "vdim"), _number(data, "scale"),
+                   None if mask is None else _positive_int(_mapping(data, "mask"), "size"))
+
+    def to_dict(self) -> dict[str, Any]:
+        data: dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale}
+        if self.chunk is not None:
+            data["mask"] = {"size": self.chunk}
+        return data
+
+
+@dataclass(frozen=True)
+class ZemavikStateSpace:
+    """The recurrent half of a ``parallel`` mixer: a state-space layer with one decay per head and step, ``heads`` heads of
+    ``vdim`` channels, a state of ``state`` rows per head, input and output maps shared by the heads of a group."""
+
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    norm_groups: int
+    conv: int
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "ZemavikStateSpace":
+        made = cls(*(_positive_int(data, key) for key in ("heads", "vdim", "state", "groups", "norm_groups", "conv")))
+        if made.heads % made.groups:
+            raise ConfigError(f"{where}: {made.heads} heads cannot be grouped over {made.groups} groups")
+        if (made.heads * made.vdim) % made.norm_groups:
+            raise ConfigError(f"{where}: {made.heads * made.vdim} channels cannot be normed in {made.norm_groups} equal parts")
+        return made
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"heads": self.heads, "vdim": self.vdim, "state": self.state, "groups": self.groups, "norm_groups": self.norm_groups,
+                "conv": self.conv}
+
+
+@dataclass(frozen=True)
+class ZemavikDelta:
+    """A ``channel_delta`` mixer: the gated delta rule with a decay per head and key channel.  The decay's and the output
+    gate's projections go through a narrow middle whose width the checkpoint's tensor shapes give (``decay_rank``,
+    ``gate_rank``; a configuration that was written for random weights names them itself)."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: Optional[int] = None
+    gate_rank: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "ZemavikDelta":
+        heads, kv_heads = _positive_int(data, "heads"), _positive_int(data, "kv_heads")
+        if heads % kv_heads:
+            raise ConfigError(f"{where}: {heads} heads cannot be grouped over {kv_heads} kv_heads")
+        ranks = [None if data.get(key) is None else _positive_int(data, key) for key in ("decay_rank", "gate_rank")]
+        return cls(heads, kv_heads, _positive_int(data, "dim"), _positive_int(data, "vdim"), _positive_int(data, "conv"), *ranks)
+
+    def to_dict(self) -> dict[str, Any]:
+        data: dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "conv": self.conv}
+        if self.decay_rank is not None:
+            data["decay_rank"] = self.decay_rank
+        if self.gate_rank is not None:
+            data["gate_rank"] = self.gate_rank
+        return data
+
+
+@dataclass(frozen=True)
+class ZemavikFeedForward:
+    """``dense``: one gated unit of inner width ``ff`` with biases.  ``moe``: ``experts`` gated units of inner width ``ff``
+    without biases, of which a token uses ``top``."""
+
+    kind: str
+    ff: int
+    experts: Optional[int] = None
+    top: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "ZemavikFeedForward":
+        kind = _require(data, "kind", str)
+        if kind == "dense":
+            return cls("dense", _positive_int(data, "ff"))
+        if kind != "moe":
+            raise ConfigError(f"{where}: unknown feed-forward kind {kind!r} (dense, moe)")
+        router = _mapping(data, "router")
+        experts, top = _positive_int(router, "experts"), _positive_int(router, "top")
+        if top > experts:
+            raise ConfigError(f"{where}: a token cannot use {top} of {experts} experts")
+        return cls("moe", _positive_int(_mapping(data, "expert"), "ff"), experts, top)
+
+    def to_dict(self) -> dict[str, Any]:
+        if self.kind == "dense":
+            return {"kind": "dense", "ff": self.ff}
+        return {"kind": "moe", "expert": {"ff": self.ff}, "router": {"experts": self.experts, "top": self.top}}
+
+
+@dataclass(frozen=True)
+class ZemavikLayer:
+    """One layer: a ``parallel`` mixer (``left`` attends, ``right`` is the state-space layer) or a ``channel_delta`` mixer, and
+    its feed-forward, or none."""
+
+    kind: str
+    left: Optional[ZemavikAttention] = None
+    right: Optional[ZemavikStateSpace] = None
+    delta: Optional[ZemavikDelta] = None
+    mlp: Optional[ZemavikFeedForward] = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], index: int) -> "ZemavikLayer":
+        kind, where = _require(data, "type", str), f"layer {index}"
+        mixer = _mapping(data, "mixer")
+        mlp = data.get("mlp")
+        if mlp is not None and not isinstance(mlp, dict):
+            raise ConfigError(f"{where}: 'mlp' must be an object or null")
+        feed_forward = None if mlp is None else ZemavikFeedForward.from_dict(mlp, where)
+        if kind == "parallel":
+            return cls(kind, left=ZemavikAttention.from_dict(_mapping(mixer, "left"), where), right=ZemavikStateSpace.from_dict(_mapping(mixer, "right"), where),
+                       mlp=feed_forward)
+        if kind == "channel_delta":
+            return cls(kind, delta=ZemavikDelta.from_dict(mixer, where), mlp=feed_forward)
+        raise ConfigError(f"{where}: unknown type {kind!r} (parallel, channel_delta)")
+
+    def to_dict(self) -> dict[str, Any]:
+        mixer = {"left": self.left.to_dict(), "right": self.right.to_dict()} if self.kind == "parallel" else self.delta.to_dict()
+        return {"type": self.kind, "mixer": mixer, "mlp": None if self.mlp is None else self.mlp.to_dict()}
+
+
+@dataclass(frozen=True)
+class ZemavikConfig:
+    """Zemavik: a decoder with a learnt vector per position added to the embedding, whose layers are, in an order the
+    configuration lists, two mixers side by side (chunked attention without positions and a state-space layer, the mean of
+    their normed outputs) or a delta rule with channel-wise decay, each with a dense gated feed-forward with biases, a
+    mixture of experts, or none; RMS norms; the head tied to the embedding; and a span of layers ``loop_start ..
+    loop_stop - 1`` that runs ``loop_times`` times in a row, every pass entered through a map of the stream and the
+    embedding output side by side (``loop`` absent: no span, no map).
+
+    ``config.json`` names the model by ``"architecture": "Zemavik"``.  Field names follow its keys.
+    """
+
+    architecture: ClassVar[str] = "Zemavik"
+
+    vocab: int
+    width: int
+    max_positions: int
+    layers: tuple[ZemavikLayer, ...]
+    norm_eps: float
+    loop: Optional[tuple[int, int, int]] = None    # (start, stop, times)
+    eos_token_ids: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if not self.layers:
+            raise ConfigError("a model needs at least one layer")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        if self.loop is not None:
+            start, stop, times = self.loop
+            if not 0 <= start < stop <= len(self.layers) or times < 1:
+                raise ConfigError(f"loop {start} .. {stop} x {times} does not fit {len(self.layers)} layers")
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "ZemavikConfig":
+        layers = _require(data, "layers", list)
+        eos = data.get("eos_token_id")
+        loop = data.get("loop")
+        if loop is not None and not isinstance(loop, dict):
+            raise ConfigError("'loop' must be an object or null")
+        return cls(
+            vocab=_positive_int(data, "vocab"),
+            width=_positive_int(data, "width"),
+            max_positions=_positive_int(data, "max_positions"),
+            layers=tuple(ZemavikLayer.from_dict(layer, index) for index, layer in enumerate(layers)),
+            norm_eps=_number(_mapping(data, "norm"), "eps"),
+            loop=None if loop is None else (int(_require(loop, "start", int)), int(_require(loop, "stop", int)), _positive_int(loop, "times")),
+            eos_token_ids=() if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(x) for x in eos)),
+        )
+
+    def to_dict(self) -> dict[str, Any]:
+        data: dict[str, Any] = {
+            "architecture": self.architecture, "vocab": self.vocab, "width": self.width, "max_positions": self.max_positions,
+            "layers": [layer.to_dict() for layer in self.layers], "norm": {"eps": self.norm_eps},
+        }
+        if self.loop is not None:
+            data["loop"] = {"start": self.loop[0], "stop": self.loop[1], "times": self.loop[2]}
+        if self.eos_token_ids:
+            data["eos_token_id"] = list(self.eos_token_ids)
+        return data
+
+    def run_order(self) -> list[tuple[int, bool]]:
+        """(layer, whether a pass of the loop starts with it) for every layer run: the layers before the loop, the loop's
+        span ``times`` times, the rest."""
+        if self.loop is None:
+            return [(index, False) for index in range(len(self.layers))]
+        start, stop, times = self.loop
+        order = [(index, False) for index in range(start)]
+        for _ in range(times):
+            order += [(index, index == start) for index in range(start, stop)]
+        return order + [(index, False) for index in range(stop, len(self.layers))]
+
+    def with_checkpoint_sizes(self, shape_of) -> "ZemavikConfig":
+        """The sizes that only tensor shapes give: ``shape_of(name)`` is a checkpoint tensor's shape, or ``None``."""
+        from dataclasses import replace
+
+        layers = []
+        for index, layer in enumerate(self.layers):
+            if layer.kind == "channel_delta":
+                decay, gate = shape_of(f"l{index}.mix.a1"), shape_of(f"l{index}.mix.g1")
+                layer = replace(layer, delta=replace(
+                    layer.delta, decay_rank=layer.delta.decay_rank if decay is None else int(decay[0]),
+                    gate_rank=layer.delta.gate_rank if gate is None else int(gate[0])))
+            layers.append(layer)
+        return replace(self, layers=tuple(layers))

@@ -1,0 +1,144 @@
+// Small kernels that stand between products:
+//   side_by_side     out[t] = [a[t] | b[t]] in the compute dtype, from two float32 blocks (the input of a map over both)
+//   gated_unit       out = act(gate + b_gate) * (up + b_up) from a product with columns [gate | up]; act = silu, relu or
+//                    the tanh form of gelu; the biases may be absent
+//   add_bias         float32 rows += a bias, in place
+//   mean_of_normed   out[t] = (1 / n) sum_i rmsnorm(y_i[t]) * w_i over n mixers' outputs of one token (each output either a
+//                    block in the compute dtype or float32 partial sums of a product cut along k), float32 out
+// All arithmetic is float32.
+#include "common.cuh"
+
+namespace pylon {
+
+template <typename T>
+__global__ void side_by_side_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int width, long long total) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= total) return;
+  const long long t = item / (2 * width);
+  const int c = (int)(item % (2 * width));
+  out[item] = from_float<T>(c < width ? a[t * width + c] : b[t * width + (c - width)]);
+}
+
+__device__ __forceinline__ float unit_activation(float x, int kind) {
+  if (kind == 0) return x / (1.f + expf(-x));                                       // silu
+  if (kind == 1) return fmaxf(x, 0.f);                                              // relu
+  return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));   // gelu, tanh form
+}
+
+template <typename T>
+__global__ void gated_unit_kernel(const T* __restrict__ gate_up, long long ld, const float* __restrict__ bias, T* __restrict__ out,
+                                  int inner, long long total, int kind) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= total) return;
+  const long long t = item / inner;
+  const int c = (int)(item % inner);
+  float g = to_float<T>(gate_up[t * ld + c]), u = to_float<T>(gate_up[t * ld + inner + c]);
+  if (bias != nullptr) { g += bias[c]; u += bias[inner + c]; }
+  out[item] = from_float<T>(unit_activation(g, kind) * u);
+}
+
+__global__ void add_bias_kernel(float* __restrict__ rows, const float* __restrict__ bias, int width, long long total) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item < total) rows[item] += bias[item % width];
+}
+
+struct NormedInput {
+  const void* data;     // [parts, T, width]
+  const float* weight;  // [width]
+  int parts;            // 1 for a plain block
+  int is_float;         // partial sums are float32; a plain block has the compute dtype
+};
+constexpr int MEAN_OF_NORMED_MAX = 4;
+struct NormedInputs { NormedInput of[MEAN_OF_NORMED_MAX]; };
+
+// A block per token.  Per input: the row is added up over its parts, its sum of squares reduced over the block, and the
+// normed row joins the mean.  A row is read twice (once for the root mean square, once for the result).
+template <typename T>
+__global__ void mean_of_normed_kernel(NormedInputs inputs, int count, float* __restrict__ out, int width, long long tokens, float eps) {
+  __shared__ float scratch[33];
+  grid_dependency_wait();
+  allow_dependents();
+  const long long t = blockIdx.x;
+  float inv[MEAN_OF_NORMED_MAX];
+  auto value = [&](const NormedInput& in, int c) {
+    float v = 0.f;
+    if (in.is_float) {
+      const float* p = (const float*)in.data + t * width + c;
+      for (int part = 0; part < in.parts; ++part) v += p[(long long)part * tokens * width];
+    } else {
+      v = to_float<T>(((const T*)in.data)[t * width + c]);
+    }
+    return v;
+  };
+  for (int i = 0; i < count; ++i) {
+    float sumsq = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float v = value(inputs.of[i], c);
+      sumsq = fmaf(v, v, sumsq);
+    }
+    inv[i] = rsqrtf(block_sum(sumsq, scratch) / (float)width + eps);
+  }
+  const float share = 1.f / (float)count;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float acc = 0.f;
+    for (int i = 0; i < count; ++i) acc += value(inputs.of[i], c) * inv[i] * inputs.of[i].weight[c];
+    out[t * width + c] = acc * share;
+  }
+}
+
+}  // namespace pylon
+
+using namespace pylon;
+
+extern "C" int pylon_side_by_side(const float* a, const float* b, void* out, int tokens, int width, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0) PYLON_REFUSE("side_by_side: width %d", width);
+  const long long total = (long long)tokens * 2 * width;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == PYLON_DTYPE_F32) launch_dependent(side_by_side_kernel<float>, grid, dim3(256), 0, stream, a, b, (float*)out, width, total);
+  else if (dtype == PYLON_DTYPE_BF16) launch_dependent(side_by_side_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, a, b, (__nv_bfloat16*)out, width, total);
+  else PYLON_REFUSE("side_by_side: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("side_by_side");
+}
+
+extern "C" int pylon_gated_unit(const void* gate_up, long long ld, const float* bias, void* out, int tokens, int inner, int kind, int dtype,
+                                cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (inner <= 0 || kind < 0 || kind > 2) PYLON_REFUSE("gated_unit: inner width %d, activation %d", inner, kind);
+  const long long total = (long long)tokens * inner;
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == PYLON_DTYPE_F32) launch_dependent(gated_unit_kernel<float>, grid, dim3(256), 0, stream, (const float*)gate_up, ld, bias, (float*)out, inner, total, kind);
+  else if (dtype == PYLON_DTYPE_BF16)
+    launch_dependent(gated_unit_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, ld, bias, (__nv_bfloat16*)out, inner, total, kind);
+  else PYLON_REFUSE("gated_unit: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("gated_unit");
+}
+
+extern "C" int pylon_add_bias(float* rows, const float* bias, long long count, int width, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (width <= 0) PYLON_REFUSE("add_bias: width %d", width);
+  const long long total = count * width;
+  launch_dependent(add_bias_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, rows, bias, width, total);
+  PYLON_CHECK_LAUNCH("add_bias");
+}
+
+// data[i]: [parts[i], tokens, width] - float32 where is_float[i], else in dtype (parts 1); weights[i]: float32 [width]; out float32 [tokens, width].
+extern "C" int pylon_mean_of_normed(const void* const* data, const float* const* weights, const int* parts, const int* is_float, int count,
+                                    float* out, int tokens, int width, float eps, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (count < 1 || count > MEAN_OF_NORMED_MAX || width <= 0) PYLON_REFUSE("mean_of_normed: %d inputs (1 to %d), width %d", count, MEAN_OF_NORMED_MAX, width);
+  NormedInputs inputs;
+  for (int i = 0; i < count; ++i) inputs.of[i] = NormedInput{data[i], weights[i], parts[i], is_float[i]};
+  const int threads = width >= 2048 ? 256 : 128;
+  if (dtype == PYLON_DTYPE_F32) launch_dependent(mean_of_normed_kernel<float>, dim3((unsigned)tokens), dim3(threads), 0, stream, inputs, count, out, width, (long long)tokens, eps);
+  else if (dtype == PYLON_DTYPE_BF16)
+    launch_dependent(mean_of_normed_kernel<__nv_bfloat16>, dim3((unsigned)tokens), dim3(threads), 0, stream, inputs, count, out, width, (long long)tokens, eps);
+  else PYLON_REFUSE("mean_of_normed: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("mean_of_normed");
+}

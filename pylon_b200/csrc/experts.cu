@@ -1,0 +1,381 @@
+// A mixture of experts: every token goes through `top` of `experts` small gated feed-forwards, chosen by a router.
+//
+//     z       = W_r h + b_r                       (float32, whatever the compute dtype)
+//     chosen  = the `top` largest z (the lower index wins a tie),   share = softmax over the chosen z only
+//     out     = sum over chosen e of share_e * W_down,e (act(W_gate,e h) * (W_up,e h))
+//
+// Nothing here needs the host to know how many tokens an expert got, so the step stays one sequence of launches (and
+// can be captured): the (token, choice) pairs are sorted by expert into row tiles of ROWS slots, every expert's span
+// padded to whole tiles, and the grouped products run over the most tiles there can be; a tile beyond the last one, and
+// a slot of padding inside a tile, is skipped.
+//
+//   experts_route     a warp per token: router logits, the top choices, their shares
+//   experts_plan      one block: tokens per expert, the experts' first tiles, a slot for every pair
+//   experts_product   a block per (row tile, column tile): rows gathered by slot, the expert's matrix, float32 sums in a
+//                     fixed order of k; with GLU the gate and up tiles side by side and act(gate) * up written
+//   experts_product_mma   the same on tensor cores (bfloat16, mma.sync m16n8k16)
+//   experts_gather    out[t] = sum_k share[t, k] * y[slot(t, k)], float32
+// A row's sums do not depend on where in a tile it lies or what else is in the batch.
+#include "common.cuh"
+#include <mma.h>
+
+namespace pylon {
+
+constexpr int EXPERT_ROWS = 32;   // slots to a row tile
+
+__device__ __forceinline__ float expert_activation(float x, int kind) {
+  if (kind == 0) return x / (1.f + expf(-x));
+  if (kind == 1) return fmaxf(x, 0.f);
+  return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+
+// h [T, width] in T; router float32 [experts, width]; bias float32 [experts] or null.  chosen int32 [T, top], share float32 [T, top].
+// Shared memory: warps * experts floats.
+template <typename T>
+__global__ void experts_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router, const float* __restrict__ bias,
+                                     int* __restrict__ chosen, float* __restrict__ share, int width, int experts, int top, int num_tokens) {
+  extern __shared__ float logits_all[];
+  grid_dependency_wait();
+  allow_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= num_tokens) return;
+  float* logits = logits_all + warp * experts;
+  const T* mine = h + (long long)t * ld;
+  constexpr int SIDE = 8;   // experts side by side: the token's row is read once per eight experts
+  for (int e0 = 0; e0 < experts; e0 += SIDE) {
+    float acc[SIDE];
+#pragma unroll
+    for (int j = 0; j < SIDE; ++j) acc[j] = 0.f;
+    for (int c = lane; c < width; c += 32) {
+      const float x = to_float<T>(mine[c]);
+#pragma unroll
+      for (int j = 0; j < SIDE; ++j)
+        if (e0 + j < experts) acc[j] = fmaf(x, router[(long long)(e0 + j) * width + c], acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < SIDE; ++j) {
+      const float z = warp_sum(acc[j]);
+      if (lane == 0 && e0 + j < experts) logits[e0 + j] = z + (bias != nullptr ? bias[e0 + j] : 0.f);
+    }
+  }
+  __syncwarp();
+  float first = 0.f, total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int where = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float z = logits[e];
+      if (z > best) { best = z; where = e; }   // strictly larger: a lane keeps its lowest index
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_where = __shfl_xor_sync(0xffffffffu, where, offset);
+      if (other > best || (other == best && other_where < where)) { best = other; where = other_where; }
+    }
+    if (where == 0x7fffffff) where = 0;   // every logit was NaN or -inf: still a valid expert
+    if (k == 0) first = best;
+    const float weight = expf(best - first);
+    total += weight;
+    if (lane == 0) {
+      chosen[(long long)t * top + k] = where;
+      share[(long long)t * top + k] = weight;
+      logits[where] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  const float inv = 1.f / total;
+  if (lane < top) share[(long long)t * top + lane] *= inv;
+  for (int k = 32 + lane; k < top; k += 32) share[(long long)t * top + k] *= inv;
+}
+
+// One block.  chosen [pairs]; slot_of [pairs] out; source [max_slots] out: the pair in a slot, or -1; tile_expert [max_tiles] out:
+// the expert of a row tile, or -1.  Shared memory: 2 * experts + 1 ints.
+__global__ void experts_plan_kernel(const int* __restrict__ chosen, int* __restrict__ slot_of, int* __restrict__ source,
+                                    int* __restrict__ tile_expert, int pairs, int experts, int max_slots, int max_tiles) {
+  extern __shared__ int plan[];
+  grid_dependency_wait();
+  allow_dependents();
+  int* count = plan;                 // tokens per expert, then the next free slot of each
+  int* first = plan + experts;       // first slot of each expert, [experts + 1]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  for (int s = threadIdx.x; s < max_slots; s += blockDim.x) source[s] = -1;
+  for (int tile = threadIdx.x; tile < max_tiles; tile += blockDim.x) tile_expert[tile] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&count[chosen[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < experts; ++e) {
+      first[e] = at;
+      at += (count[e] + EXPERT_ROWS - 1) / EXPERT_ROWS * EXPERT_ROWS;
+    }
+    first[experts] = at;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    for (int tile = first[e] / EXPERT_ROWS; tile < first[e + 1] / EXPERT_ROWS; ++tile) tile_expert[tile] = e;
+    count[e] = first[e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int slot = atomicAdd(&count[chosen[i]], 1);   // the order inside an expert's span does not matter: rows do not see each other
+    slot_of[i] = slot;
+    source[slot] = i;
+  }
+}
+
+// out[slot, n] = sum_k a[row(slot), k] * w[expert, n, k].  row(slot) = source[slot] / divide when `gathered`, else slot.
+// GLU: w is [experts, 2 * n_out, k] (gate rows, then up rows) and out[slot, n] = act(gate) * up in T; else out is float32.
+// Block 256 threads = 16 x 16; tile EXPERT_ROWS x 64; a thread owns 2 rows x 4 columns.
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256) experts_product_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ w,
+                                                              const int* __restrict__ source, const int* __restrict__ tile_expert,
+                                                              int gathered, int divide, void* __restrict__ out_v, int n_out, int k_size,
+                                                              int kind) {
+  constexpr int TN = 64, TK = 16;
+  __shared__ float a_tile[EXPERT_ROWS][TK + 1];
+  __shared__ float b_tile[GLU ? 2 : 1][TN][TK + 1];
+  __shared__ int rows[EXPERT_ROWS];
+  grid_dependency_wait();
+  allow_dependents();
+  const int tile = blockIdx.y;
+  const int expert = tile_expert[tile];
+  if (expert < 0) return;
+  const int n0 = blockIdx.x * TN;
+  if (threadIdx.x < EXPERT_ROWS) {
+    const int pair = source[tile * EXPERT_ROWS + threadIdx.x];
+    rows[threadIdx.x] = pair < 0 ? -1 : (gathered ? pair / divide : tile * EXPERT_ROWS + threadIdx.x);
+  }
+  __syncthreads();
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const long long w_rows = GLU ? 2LL * n_out : n_out;
+  const T* w_mine = w + (long long)expert * w_rows * k_size;
+  float acc[GLU ? 2 : 1][2][4];
+#pragma unroll
+  for (int g = 0; g < (GLU ? 2 : 1); ++g)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[g][i][j] = 0.f;
+  for (int k0 = 0; k0 < k_size; k0 += TK) {
+    for (int x = threadIdx.x; x < EXPERT_ROWS * TK; x += 256) {
+      const int r = x / TK, c = x % TK;
+      const int row = rows[r];
+      a_tile[r][c] = (row >= 0 && k0 + c < k_size) ? to_float<T>(a[(long long)row * lda + k0 + c]) : 0.f;
+    }
+    for (int x = threadIdx.x; x < TN * TK; x += 256) {
+      const int r = x / TK, c = x % TK;
+      const bool inside = n0 + r < n_out && k0 + c < k_size;
+      b_tile[0][r][c] = inside ? to_float<T>(w_mine[(long long)(n0 + r) * k_size + k0 + c]) : 0.f;
+      if (GLU) b_tile[1][r][c] = inside ? to_float<T>(w_mine[(long long)(n_out + n0 + r) * k_size + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < TK; ++c) {
+      float av[2], bv[GLU ? 2 : 1][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) av[i] = a_tile[ty * 2 + i][c];
+#pragma unroll
+      for (int g = 0; g < (GLU ? 2 : 1); ++g)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) bv[g][j] = b_tile[g][tx * 4 + j][c];
+#pragma unroll
+      for (int g = 0; g < (GLU ? 2 : 1); ++g)
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[g][i][j] = fmaf(av[i], bv[g][j], acc[g][i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = ty * 2 + i;
+    if (rows[r] < 0) continue;
+    const long long slot = (long long)tile * EXPERT_ROWS + r;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= n_out) continue;
+      if (GLU) ((T*)out_v)[slot * n_out + n] = from_float<T>(expert_activation(acc[0][i][j], kind) * acc[GLU ? 1 : 0][i][j]);
+      else ((float*)out_v)[slot * n_out + n] = acc[0][i][j];
+    }
+  }
+}
+
+// The same product on tensor cores for bfloat16: a block of four warps takes a row tile of 32 slots x 64 columns (with GLU: 64 gate and
+// the 64 matching up columns); warp w owns columns 16 w .. 16 w + 15 of the tile, both 16-row halves.  Steps of 32 along k through
+// shared memory (rows padded by 8 elements so that fragment loads do not collide); k_size is a multiple of 8, the rest of a step is zero.
+template <bool GLU>
+__global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfloat16* __restrict__ a, long long lda,
+                                                                  const __nv_bfloat16* __restrict__ w, const int* __restrict__ source,
+                                                                  const int* __restrict__ tile_expert, int gathered, int divide,
+                                                                  void* __restrict__ out_v, int n_out, int k_size, int kind) {
+  constexpr int TN = 64, TK = 32, PAD = 8, G = GLU ? 2 : 1;
+  __shared__ __align__(16) __nv_bfloat16 a_tile[EXPERT_ROWS][TK + PAD];
+  __shared__ __align__(16) __nv_bfloat16 b_tile[G][TN][TK + PAD];
+  __shared__ int rows[EXPERT_ROWS];
+  grid_dependency_wait();
+  allow_dependents();
+  const int tile = blockIdx.y;
+  const int expert = tile_expert[tile];
+  if (expert < 0) return;
+  const int n0 = blockIdx.x * TN;
+  if (threadIdx.x < EXPERT_ROWS) {
+    const int pair = source[tile * EXPERT_ROWS + threadIdx.x];
+    rows[threadIdx.x] = pair < 0 ? -1 : (gathered ? pair / divide : tile * EXPERT_ROWS + threadIdx.x);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = lane >> 2, quad = lane & 3;
+  const long long w_rows = GLU ? 2LL * n_out : n_out;
+  const __nv_bfloat16* w_mine = w + (long long)expert * w_rows * k_size;
+  float acc[G][2][2][4];   // [gate | up][row half][column eighth][fragment]
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int f = 0; f < 4; ++f) acc[g][i][j][f] = 0.f;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (int k0 = 0; k0 < k_size; k0 += TK) {
+    for (int x = threadIdx.x; x < EXPERT_ROWS * (TK / 8); x += 128) {
+      const int r = x / (TK / 8), c = (x % (TK / 8)) * 8;
+      const int row = rows[r];
+      *reinterpret_cast<uint4*>(&a_tile[r][c]) =
+          (row >= 0 && k0 + c < k_size) ? *reinterpret_cast<const uint4*>(a + (long long)row * lda + k0 + c) : zero;
+    }
+    for (int x = threadIdx.x; x < G * TN * (TK / 8); x += 128) {
+      const int g = x / (TN * (TK / 8)), y = x % (TN * (TK / 8));
+      const int r = y / (TK / 8), c = (y % (TK / 8)) * 8;
+      const bool inside = n0 + r < n_out && k0 + c < k_size;
+      *reinterpret_cast<uint4*>(&b_tile[g][r][c]) =
+          inside ? *reinterpret_cast<const uint4*>(w_mine + ((long long)g * n_out + n0 + r) * k_size + k0 + c) : zero;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
+      unsigned af[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        af[i][0] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group][kk + 2 * quad]);
+        af[i][1] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group + 8][kk + 2 * quad]);
+        af[i][2] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group][kk + 2 * quad + 8]);
+        af[i][3] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group + 8][kk + 2 * quad + 8]);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = 16 * warp + 8 * j + group;
+          const unsigned b0 = *reinterpret_cast<const unsigned*>(&b_tile[g][n][kk + 2 * quad]);
+          const unsigned b1 = *reinterpret_cast<const unsigned*>(&b_tile[g][n][kk + 2 * quad + 8]);
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                         : "+f"(acc[g][i][j][0]), "+f"(acc[g][i][j][1]), "+f"(acc[g][i][j][2]), "+f"(acc[g][i][j][3])
+                         : "r"(af[i][0]), "r"(af[i][1]), "r"(af[i][2]), "r"(af[i][3]), "r"(b0), "r"(b1));
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = 16 * i + group + 8 * half;
+      if (rows[r] < 0) continue;
+      const long long slot = (long long)tile * EXPERT_ROWS + r;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int n = n0 + 16 * warp + 8 * j + 2 * quad + e;
+          if (n >= n_out) continue;
+          const float value = acc[0][i][j][2 * half + e];
+          if (GLU) ((__nv_bfloat16*)out_v)[slot * n_out + n] = __float2bfloat16_rn(expert_activation(value, kind) * acc[G - 1][i][j][2 * half + e]);
+          else ((float*)out_v)[slot * n_out + n] = value;
+        }
+    }
+}
+
+// out[t, c] = sum_k share[t, k] * y[slot_of[t * top + k], c], the choices in their order.
+__global__ void experts_gather_kernel(const float* __restrict__ y, const int* __restrict__ slot_of, const float* __restrict__ share,
+                                      float* __restrict__ out, int width, int top, long long total) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= total) return;
+  const long long t = item / width;
+  const int c = (int)(item % width);
+  float acc = 0.f;
+  for (int k = 0; k < top; ++k) acc = fmaf(share[t * top + k], y[(long long)slot_of[t * top + k] * width + c], acc);
+  out[item] = acc;
+}
+
+}  // namespace pylon
+
+using namespace pylon;
+
+extern "C" int pylon_experts_row_tile() { return EXPERT_ROWS; }
+
+extern "C" int pylon_experts_route(const void* h, long long ld, const float* router, const float* bias, int* chosen, float* share, int width,
+                                   int experts, int top, int num_tokens, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (experts < 1 || top < 1 || top > experts || experts > 2048) PYLON_REFUSE("experts_route: %d of %d experts (at most 2048)", top, experts);
+  const int warps = 4;
+  const dim3 grid((unsigned)((num_tokens + warps - 1) / warps));
+  const size_t smem = (size_t)warps * experts * sizeof(float);
+  if (dtype == PYLON_DTYPE_F32)
+    launch_dependent(experts_route_kernel<float>, grid, dim3(warps * 32), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
+  else if (dtype == PYLON_DTYPE_BF16)
+    launch_dependent(experts_route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
+  else PYLON_REFUSE("experts_route: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("experts_route");
+}
+
+extern "C" int pylon_experts_plan(const int* chosen, int* slot_of, int* source, int* tile_expert, int pairs, int experts, int max_slots,
+                                  int max_tiles, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (max_slots < pairs || max_tiles * EXPERT_ROWS < max_slots) PYLON_REFUSE("experts_plan: %d slots in %d tiles for %d pairs", max_slots, max_tiles, pairs);
+  launch_dependent(experts_plan_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, chosen, slot_of, source, tile_expert,
+                   pairs, experts, max_slots, max_tiles);
+  PYLON_CHECK_LAUNCH("experts_plan");
+}
+
+// a: [rows, lda] in dtype; w: [experts, (glu ? 2 : 1) * n_out, k] in dtype, contiguous; out: [max_tiles * EXPERT_ROWS, n_out], in dtype with glu, else float32.
+extern "C" int pylon_experts_product(const void* a, long long lda, const void* w, const int* source, const int* tile_expert, int gathered,
+                                     int divide, void* out, int n_out, int k_size, int max_tiles, int glu, int kind, int dtype,
+                                     cudaStream_t stream) {
+  if (max_tiles <= 0) return 0;
+  if (n_out <= 0 || k_size <= 0 || divide < 1 || kind < 0 || kind > 2) PYLON_REFUSE("experts_product: n %d, k %d, divide %d, activation %d", n_out, k_size, divide, kind);
+  if (max_tiles > 65535) PYLON_REFUSE("experts_product: %d row tiles", max_tiles);
+  const dim3 grid((unsigned)((n_out + 63) / 64), (unsigned)max_tiles);
+  if (dtype == PYLON_DTYPE_F32) {
+    if (glu) launch_dependent(experts_product_kernel<float, true>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+    else launch_dependent(experts_product_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+  } else if (dtype == PYLON_DTYPE_BF16) {
+    const __nv_bfloat16* ab = (const __nv_bfloat16*)a;
+    const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
+    const bool vectors = k_size % 8 == 0 && lda % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0;
+    if (vectors) {
+      if (glu) launch_dependent(experts_product_mma_kernel<true>, grid, dim3(128), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+      else launch_dependent(experts_product_mma_kernel<false>, grid, dim3(128), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+    } else {
+      if (glu) launch_dependent(experts_product_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+      else launch_dependent(experts_product_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+    }
+  } else PYLON_REFUSE("experts_product: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("experts_product");
+}
+
+extern "C" int pylon_experts_gather(const float* y, const int* slot_of, const float* share, float* out, int num_tokens, int width, int top,
+                                    cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const long long total = (long long)num_tokens * width;
+  launch_dependent(experts_gather_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, slot_of, share, out, width, top, total);
+  PYLON_CHECK_LAUNCH("experts_gather");
+}

@@ -61,6 +61,9 @@ class Engine:
             self.model_dir = Path(model_dir)
             self.architecture, self.model_config = read_config(self.model_dir)
             checkpoint = Checkpoint(self.model_dir)
+            if hasattr(self.model_config, "with_checkpoint_sizes"):   # sizes that no configuration key names: the tensors' shapes give them
+                names = set(checkpoint.names())
+                self.model_config = self.model_config.with_checkpoint_sizes(lambda name: checkpoint.shape(name) if name in names else None)
         else:
             if model_config is None or random_seed is None:
                 raise ValueError("without a model folder, a model configuration and a random seed are needed")

@@ -188,7 +188,26 @@ _SIGNATURES = {
     "delta_rule.cu": {
         "pylon_gated_delta_rule": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                   c_int, c_float, c_float, c_int, c_int, c_int, c_void_p],
+                                   c_int, c_float, c_float, c_int, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p],
+    },
+    "state_space.cu": {
+        "pylon_state_space": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                              c_int, c_void_p],
+    },
+    "combine.cu": {
+        "pylon_side_by_side": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "pylon_gated_unit": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_add_bias": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+        "pylon_mean_of_normed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    },
+    "experts.cu": {
+        "pylon_experts_row_tile": [],
+        "pylon_experts_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_experts_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_experts_product": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p],
+        "pylon_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32.cu": {
         "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
@@ -1122,8 +1141,14 @@ def gated_delta_rule(
     num_rows: int,
     norm_eps: float,
     unit_eps: float = 1e-6,
+    decay_in: Optional[torch.Tensor] = None,
+    gate_in: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """The gated delta rule over the tokens of a step (see ``csrc/delta_rule.cu`` for the equations).
+
+    ``decay_in`` float32 ``[T, heads * dim]``: a decay per head and key channel, from this input (``dt_bias`` is then ``[heads * dim]``
+    and ``proj`` has no ``a`` columns).  ``gate_in`` float32 ``[T, heads * vdim]``: the output gate is its sigmoid (``proj`` then
+    has no ``gate`` columns).
 
     ``proj [T, 2 kv_heads dim + 2 heads vdim + 2 heads]``: the projections of the layer's input with columns
     ``[q | k | v | gate | a | b]``; ``conv_weight`` float32 ``[taps, channels]`` over the q, k, v columns (the last tap weighs the current token); ``state`` float32
@@ -1133,14 +1158,20 @@ def gated_delta_rule(
     normalised per head and gated, ready for the output projection."""
     _need_cuda(proj, conv_weight, state, token_row, q_start, slots, a_log, dt_bias, norm_weight)
     channels = 2 * kv_heads * dim + heads * vdim
-    columns = channels + heads * vdim + 2 * heads
-    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == columns, f"gated_delta_rule: proj must be [T, {columns}]")
+    col_gate = channels
+    col_a = col_gate + (0 if gate_in is not None else heads * vdim)
+    col_b = col_a + (0 if decay_in is not None else heads)
+    columns = col_b + heads
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] >= columns, f"gated_delta_rule: proj must be [T, {columns}] (or wider)")
     tokens = proj.shape[0]
+    for name, tensor, size in (("decay_in", decay_in, heads * dim), ("gate_in", gate_in, heads * vdim)):
+        _need(tensor is None or (tensor.is_cuda and tensor.dtype == torch.float32 and tensor.dim() == 2 and tensor.shape[0] == tokens
+                                 and tensor.shape[1] >= size and tensor.stride(1) == 1), f"gated_delta_rule: {name} must be float32 [T, {size}]")
     _need(conv_weight.dtype == torch.float32 and conv_weight.dim() == 2 and conv_weight.shape[1] == channels and conv_weight.is_contiguous(),
           "gated_delta_rule: conv_weight must be contiguous float32 [taps, channels]")
     taps = conv_weight.shape[0]
     _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous(), "gated_delta_rule: state must be contiguous float32 [slots, floats]")
-    for name, tensor, size in (("a_log", a_log, heads), ("dt_bias", dt_bias, heads), ("norm_weight", norm_weight, vdim)):
+    for name, tensor, size in (("a_log", a_log, heads), ("dt_bias", dt_bias, heads * dim if decay_in is not None else heads), ("norm_weight", norm_weight, vdim)):
         _need(tensor.dtype == torch.float32 and tensor.shape == (size,) and tensor.is_contiguous(), f"gated_delta_rule: {name} must be float32 [{size}]")
     for name, tensor, size in (("token_row", token_row, tokens), ("q_start", q_start, num_rows + 1), ("slots", slots, num_rows)):
         _need(tensor.dtype == torch.int32 and tensor.is_contiguous() and tensor.shape[0] >= size, f"gated_delta_rule: {name} must be int32 [{size}]")
@@ -1148,12 +1179,184 @@ def gated_delta_rule(
     gates = torch.empty((tokens, 2 * heads), dtype=torch.float32, device=proj.device)
     read = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=proj.device)
     out = torch.empty((tokens, heads * vdim), dtype=proj.dtype, device=proj.device)
+    decays = None if decay_in is None else torch.empty((tokens, heads * dim), dtype=torch.float32, device=proj.device)
     library = _library("delta_rule.cu")
     _check(library, library.pylon_gated_delta_rule(
         _ptr(proj), proj.stride(0), _ptr(conv_weight), taps, _ptr(state), state.shape[1], _ptr(token_row), _ptr(q_start), _ptr(slots),
-        _ptr(qkv), _ptr(gates), _ptr(read), _ptr(out), _ptr(a_log), _ptr(dt_bias), _ptr(norm_weight), channels + heads * vdim,
-        channels + heads * vdim + heads, channels, heads, kv_heads, dim, vdim, float(unit_eps), float(norm_eps), tokens, num_rows,
-        _dtype_code(proj.dtype), _stream()))
+        _ptr(qkv), _ptr(gates), _ptr(read), _ptr(out), _ptr(a_log), _ptr(dt_bias), _ptr(norm_weight), col_a, col_b, col_gate,
+        heads, kv_heads, dim, vdim, float(unit_eps), float(norm_eps), tokens, num_rows,
+        _dtype_code(proj.dtype), _ptr(decay_in), 0 if decay_in is None else decay_in.stride(0), _ptr(decays), _ptr(gate_in),
+        0 if gate_in is None else gate_in.stride(0), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# state-space mixer
+# ---------------------------------------------------------------------------------------
+def state_space(
+    proj: torch.Tensor,
+    conv_weight: torch.Tensor,
+    conv_bias: torch.Tensor,
+    state: torch.Tensor,
+    token_row: torch.Tensor,
+    q_start: torch.Tensor,
+    slots: torch.Tensor,
+    a_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    skip: torch.Tensor,
+    norm_weight: torch.Tensor,
+    heads: int,
+    groups: int,
+    state_dim: int,
+    vdim: int,
+    norm_groups: int,
+    num_rows: int,
+    norm_eps: float,
+) -> torch.Tensor:
+    """A state-space layer with one decay per head and step over the tokens of a step (``csrc/state_space.cu`` has the equations).
+
+    ``proj [T, 2 heads vdim + 2 groups N + heads]``: the projection of the layer's input with columns ``[z | x | B | C | dt]``;
+    ``conv_weight`` float32 ``[taps, channels]`` and ``conv_bias`` float32 ``[channels]`` over the x, B, C columns (the last tap weighs
+    the current token); ``state`` float32 ``[slots, heads * N * vdim + (taps - 1) * channels]``: per request the heads' matrices and
+    the convolution's last inputs, read at ``state[slots[row]]`` and advanced in place by the row's tokens; ``a_log``, ``dt_bias``,
+    ``skip`` float32 ``[heads]``; ``norm_weight`` float32 ``[heads * vdim]``.  Returns ``[T, heads * vdim]`` in ``proj``'s dtype: the
+    read-out, gated and normed in ``norm_groups`` parts, ready for the output projection."""
+    _need_cuda(proj, conv_weight, conv_bias, state, token_row, q_start, slots, a_log, dt_bias, skip, norm_weight)
+    inner = heads * vdim
+    channels = inner + 2 * groups * state_dim
+    columns = inner + channels + heads
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == columns, f"state_space: proj must be [T, {columns}]")
+    tokens = proj.shape[0]
+    _need(conv_weight.dtype == torch.float32 and conv_weight.dim() == 2 and conv_weight.shape[1] == channels and conv_weight.is_contiguous(),
+          "state_space: conv_weight must be contiguous float32 [taps, channels]")
+    taps = conv_weight.shape[0]
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous(), "state_space: state must be contiguous float32 [slots, floats]")
+    for name, tensor, size in (("a_log", a_log, heads), ("dt_bias", dt_bias, heads), ("skip", skip, heads), ("norm_weight", norm_weight, inner),
+                               ("conv_bias", conv_bias, channels)):
+        _need(tensor.dtype == torch.float32 and tensor.shape == (size,) and tensor.is_contiguous(), f"state_space: {name} must be float32 [{size}]")
+    for name, tensor, size in (("token_row", token_row, tokens), ("q_start", q_start, num_rows + 1), ("slots", slots, num_rows)):
+        _need(tensor.dtype == torch.int32 and tensor.is_contiguous() and tensor.shape[0] >= size, f"state_space: {name} must be int32 [{size}]")
+    xbc = torch.empty((tokens, channels), dtype=torch.float32, device=proj.device)
+    gates = torch.empty((tokens, 2 * heads), dtype=torch.float32, device=proj.device)
+    read = torch.empty((tokens, inner), dtype=torch.float32, device=proj.device)
+    out = torch.empty((tokens, inner), dtype=proj.dtype, device=proj.device)
+    library = _library("state_space.cu")
+    _check(library, library.pylon_state_space(
+        _ptr(proj), proj.stride(0), _ptr(conv_weight), _ptr(conv_bias), taps, _ptr(state), state.shape[1], _ptr(token_row), _ptr(q_start),
+        _ptr(slots), _ptr(xbc), _ptr(gates), _ptr(read), _ptr(out), _ptr(a_log), _ptr(dt_bias), _ptr(skip), _ptr(norm_weight), heads, groups,
+        state_dim, vdim, norm_groups, float(norm_eps), tokens, num_rows, _dtype_code(proj.dtype), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# small kernels between products
+# ---------------------------------------------------------------------------------------
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def concat_cast(a: torch.Tensor, b: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """``[a | b]`` row by row in ``dtype`` from two float32 blocks ``[T, width]``."""
+    _need_cuda(a, b)
+    _need(a.dtype == torch.float32 and b.dtype == torch.float32 and a.dim() == 2 and a.shape == b.shape and a.is_contiguous() and b.is_contiguous(),
+          "concat_cast: two contiguous float32 blocks of one shape")
+    tokens, width = a.shape
+    out = torch.empty((tokens, 2 * width), dtype=dtype, device=a.device)
+    library = _library("combine.cu")
+    _check(library, library.pylon_side_by_side(_ptr(a), _ptr(b), _ptr(out), tokens, width, _dtype_code(dtype), _stream()))
+    return out
+
+
+def gated_unit(gate_up: torch.Tensor, bias: Optional[torch.Tensor], activation: str) -> torch.Tensor:
+    """``act(gate + b_gate) * (up + b_up)`` from ``gate_up [T, 2 F]`` with columns ``[gate | up]`` and an optional float32 bias ``[2 F]``."""
+    _need_cuda(gate_up, bias)
+    _need(activation in ACTIVATIONS, f"gated_unit: activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+    _need(gate_up.dim() == 2 and gate_up.stride(1) == 1 and gate_up.shape[1] % 2 == 0, "gated_unit: gate_up must be [T, 2 F]")
+    tokens, inner = gate_up.shape[0], gate_up.shape[1] // 2
+    _need(bias is None or (bias.dtype == torch.float32 and bias.shape == (2 * inner,) and bias.is_contiguous()), "gated_unit: bias must be float32 [2 F]")
+    out = torch.empty((tokens, inner), dtype=gate_up.dtype, device=gate_up.device)
+    library = _library("combine.cu")
+    _check(library, library.pylon_gated_unit(_ptr(gate_up), gate_up.stride(0), _ptr(bias), _ptr(out), tokens, inner, ACTIVATIONS[activation],
+                                             _dtype_code(gate_up.dtype), _stream()))
+    return out
+
+
+def add_bias(rows: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """In place on float32 ``rows [..., width]``: every row plus float32 ``bias [width]``."""
+    _need_cuda(rows, bias)
+    width = bias.shape[0]
+    _need(rows.dtype == torch.float32 and rows.is_contiguous() and rows.shape[-1] == width and bias.dtype == torch.float32 and bias.is_contiguous(),
+          "add_bias: contiguous float32 rows and a float32 bias of their width")
+    library = _library("combine.cu")
+    _check(library, library.pylon_add_bias(_ptr(rows), _ptr(bias), rows.numel() // width, width, _stream()))
+    return rows
+
+
+def mean_of_normed(outputs: Sequence[torch.Tensor], weights: Sequence[torch.Tensor], eps: float, dtype: torch.dtype) -> torch.Tensor:
+    """``(1 / n) sum_i rmsnorm(y_i) * w_i`` over the width, row by row, in float32.  Each ``y_i`` is ``[T, width]`` in ``dtype`` or
+    float32 partial sums ``[parts, T, width]`` whose sum is the output (what :func:`linear_for_residual` returns); ``w_i`` float32
+    ``[width]``.  Returns float32 ``[1, T, width]``: in the form of partial sums, so that the residual stream takes it in 32-bit."""
+    _need(1 <= len(outputs) == len(weights) <= 4, "mean_of_normed: one to four outputs, a weight for each")
+    _need_cuda(*outputs, *weights)
+    tokens, width = outputs[0].shape[-2:]
+    parts, floats = [], []
+    for y, w in zip(outputs, weights):
+        _need(y.is_contiguous() and y.shape[-2:] == (tokens, width) and ((y.dim() == 3 and y.dtype == torch.float32) or (y.dim() == 2 and y.dtype == dtype)),
+              "mean_of_normed: an output is [T, width] in the compute dtype or float32 [parts, T, width]")
+        _need(w.dtype == torch.float32 and w.shape == (width,) and w.is_contiguous(), "mean_of_normed: a weight is float32 [width]")
+        parts.append(y.shape[0] if y.dim() == 3 else 1)
+        floats.append(1 if y.dtype == torch.float32 else 0)
+    count = len(outputs)
+    out = torch.empty((1, tokens, width), dtype=torch.float32, device=outputs[0].device)
+    library = _library("combine.cu")
+    _check(library, library.pylon_mean_of_normed(
+        (c_void_p * count)(*[y.data_ptr() for y in outputs]), (c_void_p * count)(*[w.data_ptr() for w in weights]), (c_int * count)(*parts),
+        (c_int * count)(*floats), count, _ptr(out), tokens, width, float(eps), _dtype_code(dtype), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# mixture of experts
+# ---------------------------------------------------------------------------------------
+def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[torch.Tensor], w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                   top: int, activation: str = "silu") -> torch.Tensor:
+    """``sum over a token's top experts e of share_e * W_down,e (act(W_gate,e h) * (W_up,e h))`` (``csrc/experts.cu``).
+
+    ``h [T, width]``; ``router`` float32 ``[experts, width]`` and ``router_bias`` float32 ``[experts]`` (or None): the logits are
+    float32 whatever ``h`` is; ``w_gate_up [experts, 2 F, width]`` (an expert's gate rows, then its up rows) and ``w_down [experts,
+    width, F]`` in ``h``'s dtype.  Returns float32 ``[1, T, width]`` (the form of partial sums: the residual stream takes it in 32-bit)."""
+    _need_cuda(h, router, router_bias, w_gate_up, w_down)
+    _need(activation in ACTIVATIONS, f"expert_mixture: activation {activation!r}")
+    _need(h.dim() == 2 and h.stride(1) == 1, "expert_mixture: h must be [T, width]")
+    tokens, width = h.shape
+    experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+    _need(w_gate_up.shape == (experts, 2 * inner, width) and w_down.shape == (experts, width, inner) and w_gate_up.is_contiguous() and w_down.is_contiguous()
+          and w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype, "expert_mixture: w_gate_up [experts, 2 F, width] and w_down [experts, width, F] in h's dtype")
+    _need(router.dtype == torch.float32 and router.shape == (experts, width) and router.is_contiguous(), "expert_mixture: router must be float32 [experts, width]")
+    _need(router_bias is None or (router_bias.dtype == torch.float32 and router_bias.shape == (experts,)), "expert_mixture: router_bias must be float32 [experts]")
+    _need(1 <= top <= experts, f"expert_mixture: top {top} of {experts} experts")
+    library = _library("experts.cu")
+    tile = library.pylon_experts_row_tile()
+    pairs = tokens * top
+    max_tiles = min(pairs, experts) + pairs // tile    # every expert with tokens ends in at most one partly filled tile
+    max_slots = max_tiles * tile
+    device = h.device
+    chosen = torch.empty((tokens, top), dtype=torch.int32, device=device)
+    share = torch.empty((tokens, top), dtype=torch.float32, device=device)
+    slot_of = torch.empty((pairs,), dtype=torch.int32, device=device)
+    source = torch.empty((max_slots,), dtype=torch.int32, device=device)
+    tile_expert = torch.empty((max_tiles,), dtype=torch.int32, device=device)
+    code, kind = _dtype_code(h.dtype), ACTIVATIONS[activation]
+    _check(library, library.pylon_experts_route(_ptr(h), h.stride(0), _ptr(router), _ptr(router_bias), _ptr(chosen), _ptr(share), width, experts, top,
+                                                tokens, code, _stream()))
+    _check(library, library.pylon_experts_plan(_ptr(chosen), _ptr(slot_of), _ptr(source), _ptr(tile_expert), pairs, experts, max_slots, max_tiles, _stream()))
+    act = torch.empty((max_slots, inner), dtype=h.dtype, device=device)
+    _check(library, library.pylon_experts_product(_ptr(h), h.stride(0), _ptr(w_gate_up), _ptr(source), _ptr(tile_expert), 1, top, _ptr(act), inner, width,
+                                                  max_tiles, 1, kind, code, _stream()))
+    y = torch.empty((max_slots, width), dtype=torch.float32, device=device)
+    _check(library, library.pylon_experts_product(_ptr(act), inner, _ptr(w_down), _ptr(source), _ptr(tile_expert), 0, 1, _ptr(y), width, inner,
+                                                  max_tiles, 0, kind, code, _stream()))
+    out = torch.empty((1, tokens, width), dtype=torch.float32, device=device)
+    _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, _stream()))
     return out
 
 

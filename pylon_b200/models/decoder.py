@@ -27,6 +27,8 @@ class DecoderModel:
         self.final_norm = NORMS.build(spec.final_norm)
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
+        self.position_table: Optional[torch.Tensor] = None   # learnt vectors per position, added to the embedding rows
+        self.reentry: Optional[torch.Tensor] = None          # [width, 2 width]: how a run with ``reenter`` is entered
         self.dtype: Optional[torch.dtype] = None
         self.device: Optional[torch.device] = None
 
@@ -37,6 +39,10 @@ class DecoderModel:
         decls = {spec.embedding_name: TensorDecl(spec.embedding_name, (spec.vocab_size, spec.width))}
         if spec.lm_head_name is not None:
             decls[spec.lm_head_name] = TensorDecl(spec.lm_head_name, (spec.vocab_size, spec.width))
+        if spec.position_name is not None:
+            decls[spec.position_name] = TensorDecl(spec.position_name, (spec.position_rows, spec.width))
+        if spec.reentry_name is not None:
+            decls[spec.reentry_name] = TensorDecl(spec.reentry_name, (spec.width, 2 * spec.width), "matrix", (0.0, (2 * spec.width) ** -0.5))
         for decl in self.final_norm.tensors():
             name = spec.final_norm_prefix + decl.name
             decls[name] = TensorDecl(name, decl.shape, decl.role, decl.init)
@@ -61,6 +67,10 @@ class DecoderModel:
         decls = self.tensor_decls()
         self.embedding = place(decls[spec.embedding_name]).contiguous()
         self.lm_head = self.embedding if spec.lm_head_name is None else place(decls[spec.lm_head_name]).contiguous()
+        if spec.position_name is not None:
+            self.position_table = place(decls[spec.position_name]).contiguous()
+        if spec.reentry_name is not None:
+            self.reentry = place(decls[spec.reentry_name]).contiguous()
         self.final_norm.load(
             {decl.name: place(decls[spec.final_norm_prefix + decl.name]) for decl in self.final_norm.tensors()}, dtype, self.device
         )
@@ -72,6 +82,8 @@ class DecoderModel:
         total = self.lm_head.numel() * self.lm_head.element_size() + self.final_norm.weight_bytes()
         for run in self.spec.order:
             total += self.blocks[run.layer].weight_bytes()
+            if run.reenter:
+                total += self.reentry.numel() * self.reentry.element_size()
         return total
 
     def takes_padding(self) -> bool:
@@ -96,8 +108,16 @@ class DecoderModel:
         (the sum of the copies where the model keeps several) - for looking at a model layer by layer."""
         step.carry = {}
         residual = ops.embed_gather(step.token_ids, self.embedding, scale=self.spec.embedding_scale, copies=self.spec.streams)
+        if self.position_table is not None:   # the learnt vector of each token's position joins its embedding row, in 32-bit like the sum
+            ops.embed_gather(step.positions, self.position_table, out=residual, copies=self.spec.streams, accumulate=True)
+        entered = residual.clone() if self.reentry is not None else None   # the embedding output, for the runs that re-enter
         stream = ResidualStream(residual)
         for position, run in enumerate(self.spec.order):
+            if run.reenter:
+                # x <- W [x; x0]: what is pending joins the sum, both halves are laid side by side in the compute dtype, and the
+                # product's 32-bit result is the new sum
+                stream.flush()
+                stream.residual = ops.linear(ops.concat_cast(stream.residual, entered, self.dtype), self.reentry, out_dtype=torch.float32)
             if run.add_embedding:
                 stream.flush()   # what the run before left pending joins the sum first; then the embedding rows, in 32-bit like the sum itself
                 ops.embed_gather(step.token_ids, self.embedding, out=stream.residual, scale=self.spec.embedding_scale, copies=self.spec.streams,

@@ -64,3 +64,100 @@ class ClampedGLU(SwiGLU):
 
     def __init__(self, width: int, intermediate: int, limit: float, alpha: float = 1.702, names: Optional[Mapping[str, str]] = None) -> None:
         super().__init__(width, intermediate, names, limit=limit, alpha=alpha)
+
+
+@FEED_FORWARDS.register("gated_unit")
+class GatedUnit(FeedForward):
+    """``down(act(gate(x)) * up(x))`` with a named activation (``silu``, ``relu``, ``gelu_tanh``) and optional biases on all three
+    projections (their tensors are the weights' names with ``bias_suffix``).  Gate and up are one product; biases, activation and
+    the product of the two halves are one float32 kernel behind it; the down projection's bias joins its 32-bit result."""
+
+    def __init__(self, width: int, intermediate: int, activation: str = "silu", bias: bool = False, bias_suffix: str = ".b",
+                 names: Optional[Mapping[str, str]] = None) -> None:
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r} (known: {', '.join(ops.ACTIVATIONS)})")
+        self.width, self.intermediate, self.activation = int(width), int(intermediate), activation
+        self.bias, self.bias_suffix = bool(bias), bias_suffix
+        self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
+        self.w_gate_up = self.w_down = self.b_gate_up = self.b_down = None
+        self.fused = False
+
+    def tensors(self) -> Sequence[TensorDecl]:
+        n = self.names
+        decls = [TensorDecl(n["gate"], (self.intermediate, self.width)), TensorDecl(n["up"], (self.intermediate, self.width)),
+                 TensorDecl(n["down"], (self.width, self.intermediate))]
+        if self.bias:
+            decls += [TensorDecl(n[key] + self.bias_suffix, (size,), "vector", (0.0, 0.02))
+                      for key, size in (("gate", self.intermediate), ("up", self.intermediate), ("down", self.width))]
+        return decls
+
+    def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        n = self.names
+        # silu without biases is the unit the products' own epilogues apply (rows of gate and up in turn, in groups of 8)
+        self.fused = self.activation == "silu" and not self.bias and dtype == torch.bfloat16 and self.intermediate % 8 == 0
+        if self.fused:
+            self.w_gate_up = ops.interleave_gate_up(tensors[n["gate"]], tensors[n["up"]])
+        else:
+            self.w_gate_up = torch.cat((tensors[n["gate"]], tensors[n["up"]]), dim=0).contiguous()
+        self.w_down = tensors[n["down"]].contiguous()
+        if self.bias:
+            self.b_gate_up = torch.cat((tensors[n["gate"] + self.bias_suffix], tensors[n["up"] + self.bias_suffix])).contiguous()
+            self.b_down = tensors[n["down"] + self.bias_suffix].contiguous()
+
+    def weight_bytes(self) -> int:
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size() + (4 * (2 * self.intermediate + self.width) if self.bias else 0)
+
+    def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
+        if self.fused:
+            return ops.linear_for_residual(ops.linear_swiglu(h, self.w_gate_up), self.w_down)
+        activation = ops.gated_unit(ops.linear(h, self.w_gate_up), self.b_gate_up, self.activation)
+        if not self.bias:
+            return ops.linear_for_residual(activation, self.w_down)
+        out = ops.linear(activation, self.w_down, out_dtype=torch.float32)
+        return ops.add_bias(out, self.b_down).unsqueeze(0)   # float32, in the form of partial sums: the stream takes it in 32-bit
+
+
+@FEED_FORWARDS.register("expert_mixture")
+class ExpertMixture(FeedForward):
+    """A mixture of experts: ``experts`` gated units ``down_e(act(gate_e(x)) * up_e(x))`` without biases, of which every token
+    goes through the ``top`` whose router logits ``W_r x (+ b_r)`` are largest, weighted by the softmax over just those logits.
+    The router's weights stay float32 and its logits are float32 sums whatever the compute dtype.  An expert's tensors are
+    ``e<i>.gate`` / ``.up`` / ``.down``; they are stacked at load, and the tokens of a step are sorted by expert on the device
+    (``csrc/experts.cu``), so a step is the same sequence of launches whatever the routing."""
+
+    def __init__(self, width: int, intermediate: int, experts: int, top: int, activation: str = "silu", router_bias: bool = False,
+                 names: Optional[Mapping[str, str]] = None) -> None:
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r} (known: {', '.join(ops.ACTIVATIONS)})")
+        self.width, self.intermediate, self.experts, self.top = int(width), int(intermediate), int(experts), int(top)
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"a token cannot use {top} of {experts} experts")
+        self.activation, self.router_bias = activation, bool(router_bias)
+        self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}.", "gate": "gate", "up": "up", "down": "down", **(names or {})}
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+
+    def _expert(self, index: int, key: str) -> str:
+        return self.names["expert"].format(index) + self.names[key]
+
+    def tensors(self) -> Sequence[TensorDecl]:
+        decls = []
+        for e in range(self.experts):
+            decls += [TensorDecl(self._expert(e, "gate"), (self.intermediate, self.width)), TensorDecl(self._expert(e, "up"), (self.intermediate, self.width)),
+                      TensorDecl(self._expert(e, "down"), (self.width, self.intermediate))]
+        decls.append(TensorDecl(self.names["router"], (self.experts, self.width), "vector", (0.0, 0.5)))
+        if self.router_bias:
+            decls.append(TensorDecl(self.names["router_bias"], (self.experts,), "vector", (0.0, 0.1)))
+        return decls
+
+    def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        self.w_gate_up = torch.stack([torch.cat((tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]), dim=0) for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
+        self.w_router = tensors[self.names["router"]].contiguous()
+        self.b_router = tensors[self.names["router_bias"]].contiguous() if self.router_bias else None
+
+    def weight_bytes(self) -> int:
+        """What a step of many tokens reads: every expert (a step of few tokens reads ``top`` experts a token at most)."""
+        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size() + self.w_router.numel() * 4
+
+    def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
+        return ops.expert_mixture(h, self.w_router, self.b_router, self.w_gate_up, self.w_down, self.top, self.activation)

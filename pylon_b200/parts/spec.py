@@ -45,12 +45,15 @@ class RunSpec:
     means this run owns its own (sized by what its mixer says it needs).  ``add_embedding``: right
     before this run the step's embedding rows (scaled as they entered the stream) are added to the
     residual stream once more - what a model does that runs a span of layers several times and feeds
-    its input in again at the start of every further pass.
+    its input in again at the start of every further pass.  ``reenter``: right before this run the stream is replaced by
+    ``W [x; x0]``, x being the stream and x0 the embedding output of the step's tokens, both ``width`` wide, W the model's
+    ``reentry_name`` tensor ``[width, 2 width]`` - how a pass of a looped span is entered.
     """
 
     layer: int
     cache_of: Optional[int] = None
     add_embedding: bool = False
+    reenter: bool = False
 
 
 @dataclass(frozen=True)
@@ -70,6 +73,9 @@ class ModelSpec:
     logit_scale: float = 1.0                # the logits are multiplied by it,
     logit_softcap: Optional[float] = None   # then, with a cap c, squashed to c * tanh(logit / c)
     streams: int = 1                        # copies of the residual stream (hyper-connections); all start as the embedding row
+    position_name: Optional[str] = None     # checkpoint name of a learnt table [position_rows, width]: row p is added to the embedding of the token at position p
+    position_rows: int = 0
+    reentry_name: Optional[str] = None      # checkpoint name of the [width, 2 width] matrix that runs with ``reenter`` go through
 
     def __post_init__(self) -> None:
         runs = tuple(run if isinstance(run, RunSpec) else RunSpec(int(run)) for run in self.order)
@@ -77,6 +83,10 @@ class ModelSpec:
         object.__setattr__(self, "layers", tuple(self.layers))
         if not runs:
             raise ValueError("a model must run at least one layer")
+        if any(run.reenter for run in runs) and (self.reentry_name is None or self.streams != 1):
+            raise ValueError("a run that re-enters needs the model's reentry matrix and a residual stream of one copy")
+        if self.position_name is not None and not 0 < self.max_positions <= self.position_rows:
+            raise ValueError(f"{self.max_positions} positions, but the table of learnt positions has {self.position_rows} rows")
         for position, run in enumerate(runs):
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"run {position} names layer {run.layer}, but there are {len(self.layers)} layers")
