@@ -18,8 +18,8 @@ decode steps) at B = 1, 8, 64 with its share of the HBM roofline; the output rat
 serving workloads at the 8B and 14B shapes; and a full-depth float32 run at the 14B shape with
 its largest logit error against the plain implementation.
 
-``--workload designs`` is another measurement with a line of its own: Vopepel and Fikerax beside Qwen3 dense at equal width, depth,
-heads, feed-forward and vocabulary (sizes ``2k`` and ``4k``; ``--designs`` picks among the three): prefill of a 2,048-token prompt, decode at batch 8 and a context of 2,048,
+``--workload designs`` is another measurement with a line of its own: Vopepel, Fikerax and Zemavik beside Qwen3 dense at equal width, depth,
+heads, feed-forward and vocabulary (sizes ``2k`` and ``4k``; ``--designs`` picks among the four): prefill of a 2,048-token prompt, decode at batch 8 and a context of 2,048,
 and the time of every kernel entry point in one step of each kind.
 """
 from __future__ import annotations
@@ -475,7 +475,7 @@ def run_serving_workload(name: str, torch) -> dict:
 
 
 # ---------------------------------------------------------------------------------------
-# Vopepel and Fikerax beside Qwen3 at equal size (--workload designs)
+# Vopepel, Fikerax and Zemavik beside Qwen3 at equal size (--workload designs)
 # ---------------------------------------------------------------------------------------
 DESIGN_SIZES = {
     # width, layers, heads / kv heads / head size of the attention, inner width of the feed-forward, vocabulary
@@ -485,8 +485,9 @@ DESIGN_SIZES = {
 DESIGN_CONTEXT = 2_048
 _TIMED_OPS = ("linear", "linear_for_residual", "linear_swiglu", "linear_for_rotation", "linear_qkv_rotated", "paged_attention", "gated_delta_rule",
               "streams_update_norm", "add_rmsnorm", "swiglu", "qk_norm_mix_kv_write", "qk_norm_rope_kv_write", "embed_gather", "lightning_attention",
-              "qkv_rotate_write", "latent_norm_rotate_write", "rotate_heads", "linear_heads")
-DESIGNS = ("vopepel", "qwen3", "fikerax")
+              "qkv_rotate_write", "latent_norm_rotate_write", "rotate_heads", "linear_heads", "state_space", "expert_mixture", "mean_of_normed",
+              "gated_unit", "add_bias", "concat_cast")
+DESIGNS = ("vopepel", "qwen3", "fikerax", "zemavik")
 
 
 def vopepel_fields(size: dict) -> dict:
@@ -523,6 +524,25 @@ def fikerax_fields(size: dict) -> dict:
             "rot": {"dims": dim, "base": 500_000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8_192}}}}
     return {"architecture": "Fikerax", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": size["width"] ** 0.5}, "norm": {"eps": 1e-5},
             "loop": {"start": 0, "stop": 0, "times": 1}, "layers": [layer(index) for index in range(size["layers"])]}
+
+
+def zemavik_fields(size: dict) -> dict:
+    """A Zemavik model of the given size: of every four layers the third is a delta rule with a decay per key channel (narrow
+    middles of 128), the others attention in chunks of 1,024 positions beside a state-space layer as wide as the model (heads of
+    64 channels, 128 state rows, a convolution of 4 taps); every other layer's feed-forward is a mixture of 8 experts of half the
+    inner width of which a token uses 2, so that a token's products are the dense layer's; the loop spans every layer once, so the
+    depth is the other designs' and the map into the loop is in the step."""
+    def layer(index: int) -> dict:
+        mlp = {"kind": "moe", "expert": {"ff": size["ff"] // 2}, "router": {"experts": 8, "top": 2}} if index % 2 else {"kind": "dense", "ff": size["ff"]}
+        heads, dim = size["heads"], size["head_dim"]
+        if index % 4 == 2:
+            return {"type": "channel_delta", "mlp": mlp, "mixer": {"heads": heads, "kv_heads": heads // 2, "dim": dim, "vdim": dim, "conv": 4,
+                                                                   "decay_rank": 128, "gate_rank": 128}}
+        return {"type": "parallel", "mlp": mlp, "mixer": {
+            "left": {"heads": heads, "kv_heads": size["kv_heads"], "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": 1_024}},
+            "right": {"heads": size["width"] // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}}
+    return {"architecture": "Zemavik", "vocab": size["vocab"], "width": size["width"], "max_positions": 4_096, "norm": {"eps": 1e-5},
+            "loop": {"start": 0, "stop": size["layers"], "times": 1}, "layers": [layer(index) for index in range(size["layers"])]}
 
 
 def qwen3_fields(size: dict) -> dict:
@@ -641,20 +661,20 @@ def time_design(engine, torch, ops, rng, batch: int, steps: int) -> dict:
 
 
 def run_design_comparison(torch, sizes, batch: int, steps: int, designs=DESIGNS) -> dict:
-    """Vopepel, Fikerax and Qwen3 dense at equal width, depth, heads, feed-forward and vocabulary: prefill and decode throughput
+    """Vopepel, Fikerax, Zemavik and Qwen3 dense at equal width, depth, heads, feed-forward and vocabulary: prefill and decode throughput
     and the time of every kernel entry point, random weights."""
     import gc
 
     import numpy as np
 
     from pylon_b200.config import EngineConfig, Qwen3Config
-    from pylon_b200.config.model_config import FikeraxConfig, VopepelConfig
+    from pylon_b200.config.model_config import FikeraxConfig, VopepelConfig, ZemavikConfig
     from pylon_b200.engine import Engine
     from pylon_b200.kernels import ops
 
     peak = peaks()
     made = {"vopepel": lambda size: VopepelConfig.from_dict(vopepel_fields(size)), "qwen3": lambda size: Qwen3Config(**qwen3_fields(size)),
-            "fikerax": lambda size: FikeraxConfig.from_dict(fikerax_fields(size))}
+            "fikerax": lambda size: FikeraxConfig.from_dict(fikerax_fields(size)), "zemavik": lambda size: ZemavikConfig.from_dict(zemavik_fields(size))}
     record = {"metric": "prefill and decode, " + ", ".join(designs) + " at equal size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
               "data": "synthetic: random weights, uniform random token ids, caches filled by real prefill",
               "config": {"prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "decode_context": DESIGN_CONTEXT, "decode_steps": steps,
@@ -731,7 +751,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     parser.add_argument("--workload", choices=["decode4b", "mixed8b", "sampled14b", "designs"], default="decode4b",
                         help="decode4b: the headline measurement (default); mixed8b, sampled14b: the serving workloads of the 8B and 14B shapes; "
-                             "designs: Vopepel and Fikerax beside Qwen3 at equal size, prefill and decode with the time of every kernel entry point")
+                             "designs: Vopepel, Fikerax and Zemavik beside Qwen3 at equal size, prefill and decode with the time of every kernel entry point")
     parser.add_argument("--design-sizes", default="2k,4k", help="with --workload designs: which of the sizes 2k, 4k")
     parser.add_argument("--designs", default=",".join(DESIGNS), help="with --workload designs: which of " + ", ".join(DESIGNS))
     parser.add_argument("--profile", choices=["decode", "prefill"],

@@ -655,7 +655,7 @@ class ZemavikConfig:
             raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
         if self.loop is not None:
             start, stop, times = self.loop
-            if not 0 <= start < stop <= len(self.layers) or times < 1:
+            if not 0 <= start <= stop <= len(self.layers) or times < 1:    # start = stop: an empty span, nothing runs twice
                 raise ConfigError(f"loop {start} .. {stop} x {times} does not fit {len(self.layers)} layers")
 
     @classmethod

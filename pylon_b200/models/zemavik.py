@@ -82,5 +82,5 @@ def zemavik_spec(config: ZemavikConfig, max_positions: Optional[int] = None) -> 
         eos_token_ids=config.eos_token_ids,
         position_name="pos",
         position_rows=config.max_positions,
-        reentry_name="loop.in" if config.loop is not None else None,
+        reentry_name="loop.in" if any(starts for _, starts in config.run_order()) else None,
     )

@@ -63,9 +63,21 @@ def route(h: torch.Tensor, router: torch.Tensor, router_b: torch.Tensor, top: in
     return chosen.indices, torch.softmax(chosen.values, dim=-1)
 
 
-def expert_mixture(h: torch.Tensor, weights: Mapping[str, torch.Tensor], prefix: str, experts: int, top: int) -> torch.Tensor:
+def route_margin(h: torch.Tensor, router: torch.Tensor, router_b: torch.Tensor, top: int) -> torch.Tensor:
+    """Per token, how far the last chosen logit lies above the best one that is left out (infinite when none is left out):
+    a choice with a small margin may go the other way under rounding."""
+    logits = torch.sort(h @ router.T + router_b, dim=-1, descending=True).values
+    if top >= logits.shape[-1]:
+        return torch.full(logits.shape[:-1], math.inf, dtype=h.dtype)
+    return logits[..., top - 1] - logits[..., top]
+
+
+def expert_mixture(h: torch.Tensor, weights: Mapping[str, torch.Tensor], prefix: str, experts: int, top: int,
+                   margins: Optional[list] = None) -> torch.Tensor:
     """Token by token: the weighted sum of its chosen experts, each ``down(silu(gate h) * (up h))`` without biases."""
     which, share = route(h, weights[prefix + "router"], weights[prefix + "router.b"], top)
+    if margins is not None:
+        margins.append(route_margin(h, weights[prefix + "router"], weights[prefix + "router.b"], top))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for slot in range(top):
@@ -171,7 +183,7 @@ def run_order(config: Mapping) -> list[tuple[int, bool]]:
     return order + [(i, False) for i in range(loop["stop"], count)]
 
 
-def layer(x, config: Mapping, w: Mapping[str, torch.Tensor], index: int) -> torch.Tensor:
+def layer(x, config: Mapping, w: Mapping[str, torch.Tensor], index: int, margins: Optional[list] = None) -> torch.Tensor:
     entry, eps, prefix = config["layers"][index], config["norm"]["eps"], f"l{index}."
     h = rms_norm(x, w[prefix + "norm1"], eps)
     mixer = entry["mixer"]
@@ -188,11 +200,13 @@ def layer(x, config: Mapping, w: Mapping[str, torch.Tensor], index: int) -> torc
     p = prefix + "mlp."
     if mlp["kind"] == "dense":
         return x + dense_relu_glu(h, w[p + "gate"], w[p + "gate.b"], w[p + "up"], w[p + "up.b"], w[p + "down"], w[p + "down.b"])
-    return x + expert_mixture(h, w, p, mlp["router"]["experts"], mlp["router"]["top"])
+    return x + expert_mixture(h, w, p, mlp["router"]["experts"], mlp["router"]["top"], margins)
 
 
-def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype: torch.dtype = torch.float64, taps: Optional[list] = None) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of one sequence from position 0.  ``taps`` receives the residual stream after every layer run."""
+def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype: torch.dtype = torch.float64, taps: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one sequence from position 0.  ``taps`` receives the residual stream after every layer run,
+    ``margins`` the routers' margins ``[T]`` of every run of a layer with experts."""
     w = {name: (t.to(dtype) if t.is_floating_point() else t) for name, t in weights.items()}
     ids = torch.as_tensor(tokens, dtype=torch.long)
     x0 = w["embed"][ids] + w["pos"][: len(ids)]
@@ -200,7 +214,7 @@ def forward(config: Mapping, weights: Mapping[str, torch.Tensor], tokens, dtype:
     for index, starts_pass in run_order(config):
         if starts_pass:
             x = torch.cat([x, x0], dim=-1) @ w["loop.in"].T
-        x = layer(x, config, w, index)
+        x = layer(x, config, w, index, margins)
         if taps is not None:
             taps.append(x.clone())
     return rms_norm(x, w["final.norm"], config["norm"]["eps"]) @ w["embed"].T
