@@ -29,6 +29,12 @@ __device__ __forceinline__ float expert_activation(float x, int kind) {
   return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 
+// The row of w that holds column n of the gate (half 0) or of the up projection (half 1): the two halves one after the other, or
+// (interleaved) alternating in groups of 8 rows, the layout the tcgen05 product's gated epilogue takes.
+__device__ __forceinline__ long long glu_row(int n, int half, int n_out, int interleaved) {
+  return interleaved ? ((long long)(n >> 3) << 4) + (half << 3) + (n & 7) : (long long)half * n_out + n;
+}
+
 // h [T, width] in T; router float32 [experts, width]; bias float32 [experts] or null.  chosen int32 [T, top], share float32 [T, top].
 // Shared memory: warps * experts floats.
 template <typename T>
@@ -90,9 +96,9 @@ __global__ void experts_route_kernel(const T* __restrict__ h, long long ld, cons
 }
 
 // One block.  chosen [pairs]; slot_of [pairs] out; source [max_slots] out: the pair in a slot, or -1; tile_expert [max_tiles] out:
-// the expert of a row tile, or -1.  Shared memory: 2 * experts + 1 ints.
+// the expert of a row tile of tile_rows slots, or -1.  Shared memory: 2 * experts + 1 ints.
 __global__ void experts_plan_kernel(const int* __restrict__ chosen, int* __restrict__ slot_of, int* __restrict__ source,
-                                    int* __restrict__ tile_expert, int pairs, int experts, int max_slots, int max_tiles) {
+                                    int* __restrict__ tile_expert, int pairs, int experts, int max_slots, int max_tiles, int tile_rows) {
   extern __shared__ int plan[];
   grid_dependency_wait();
   allow_dependents();
@@ -108,13 +114,13 @@ __global__ void experts_plan_kernel(const int* __restrict__ chosen, int* __restr
     int at = 0;
     for (int e = 0; e < experts; ++e) {
       first[e] = at;
-      at += (count[e] + EXPERT_ROWS - 1) / EXPERT_ROWS * EXPERT_ROWS;
+      at += (count[e] + tile_rows - 1) / tile_rows * tile_rows;
     }
     first[experts] = at;
   }
   __syncthreads();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
-    for (int tile = first[e] / EXPERT_ROWS; tile < first[e + 1] / EXPERT_ROWS; ++tile) tile_expert[tile] = e;
+    for (int tile = first[e] / tile_rows; tile < first[e + 1] / tile_rows; ++tile) tile_expert[tile] = e;
     count[e] = first[e];
   }
   __syncthreads();
@@ -132,7 +138,7 @@ template <typename T, bool GLU>
 __global__ void __launch_bounds__(256) experts_product_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ w,
                                                               const int* __restrict__ source, const int* __restrict__ tile_expert,
                                                               int gathered, int divide, void* __restrict__ out_v, int n_out, int k_size,
-                                                              int kind) {
+                                                              int kind, int interleaved) {
   constexpr int TN = 64, TK = 16;
   __shared__ float a_tile[EXPERT_ROWS][TK + 1];
   __shared__ float b_tile[GLU ? 2 : 1][TN][TK + 1];
@@ -167,8 +173,8 @@ __global__ void __launch_bounds__(256) experts_product_kernel(const T* __restric
     for (int x = threadIdx.x; x < TN * TK; x += 256) {
       const int r = x / TK, c = x % TK;
       const bool inside = n0 + r < n_out && k0 + c < k_size;
-      b_tile[0][r][c] = inside ? to_float<T>(w_mine[(long long)(n0 + r) * k_size + k0 + c]) : 0.f;
-      if (GLU) b_tile[1][r][c] = inside ? to_float<T>(w_mine[(long long)(n_out + n0 + r) * k_size + k0 + c]) : 0.f;
+      b_tile[0][r][c] = inside ? to_float<T>(w_mine[glu_row(n0 + r, 0, n_out, GLU && interleaved) * k_size + k0 + c]) : 0.f;
+      if (GLU) b_tile[1][r][c] = inside ? to_float<T>(w_mine[glu_row(n0 + r, 1, n_out, interleaved) * k_size + k0 + c]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -205,16 +211,29 @@ __global__ void __launch_bounds__(256) experts_product_kernel(const T* __restric
 }
 
 // The same product on tensor cores for bfloat16: a block of four warps takes a row tile of 32 slots x 64 columns (with GLU: 64 gate and
-// the 64 matching up columns); warp w owns columns 16 w .. 16 w + 15 of the tile, both 16-row halves.  Steps of 32 along k through
-// shared memory (rows padded by 8 elements so that fragment loads do not collide); k_size is a multiple of 8, the rest of a step is zero.
+// the 64 matching up columns); warp w owns columns 16 w .. 16 w + 15 of the tile, both 16-row halves.  Steps of 64 along k through a ring
+// of MMA_STAGES shared-memory stages that cp.async fills ahead of the products (a step of few tokens is bound by the experts' matrices
+// coming from memory, so several steps' loads are kept in flight); rows padded by 8 elements so that fragment loads do not collide;
+// k_size is a multiple of 8, the rest of a step and the rows of empty slots are filled with zeros.
+constexpr int MMA_TN = 64, MMA_TK = 64, MMA_PAD = 8, MMA_STAGES = 4;
+__host__ __device__ constexpr int mma_stage_elements(bool glu) { return (EXPERT_ROWS + (glu ? 2 : 1) * MMA_TN) * (MMA_TK + MMA_PAD); }
+constexpr size_t mma_shared_bytes(bool glu) { return (size_t)MMA_STAGES * mma_stage_elements(glu) * sizeof(__nv_bfloat16); }
+
+__device__ __forceinline__ void copy_16_or_zeros(void* shared, const void* global, bool real) {
+  const unsigned target = (unsigned)__cvta_generic_to_shared(shared);
+  const int bytes = real ? 16 : 0;   // what is not copied is written as zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(target), "l"(global), "r"(bytes) : "memory");
+}
+
 template <bool GLU>
 __global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfloat16* __restrict__ a, long long lda,
                                                                   const __nv_bfloat16* __restrict__ w, const int* __restrict__ source,
                                                                   const int* __restrict__ tile_expert, int gathered, int divide,
-                                                                  void* __restrict__ out_v, int n_out, int k_size, int kind) {
-  constexpr int TN = 64, TK = 32, PAD = 8, G = GLU ? 2 : 1;
-  __shared__ __align__(16) __nv_bfloat16 a_tile[EXPERT_ROWS][TK + PAD];
-  __shared__ __align__(16) __nv_bfloat16 b_tile[G][TN][TK + PAD];
+                                                                  void* __restrict__ out_v, int n_out, int k_size, int kind, int interleaved) {
+  constexpr int TN = MMA_TN, TK = MMA_TK, LD = MMA_TK + MMA_PAD, G = GLU ? 2 : 1;
+  constexpr int A_ELEMENTS = EXPERT_ROWS * LD, STAGE_ELEMENTS = mma_stage_elements(GLU);
+  extern __shared__ __align__(16) unsigned char mma_shared[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(mma_shared);
   __shared__ int rows[EXPERT_ROWS];
   grid_dependency_wait();
   allow_dependents();
@@ -240,39 +259,52 @@ __global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfl
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int f = 0; f < 4; ++f) acc[g][i][j][f] = 0.f;
-  const uint4 zero = make_uint4(0, 0, 0, 0);
-  for (int k0 = 0; k0 < k_size; k0 += TK) {
-    for (int x = threadIdx.x; x < EXPERT_ROWS * (TK / 8); x += 128) {
-      const int r = x / (TK / 8), c = (x % (TK / 8)) * 8;
-      const int row = rows[r];
-      *reinterpret_cast<uint4*>(&a_tile[r][c]) =
-          (row >= 0 && k0 + c < k_size) ? *reinterpret_cast<const uint4*>(a + (long long)row * lda + k0 + c) : zero;
+  const int steps = (k_size + TK - 1) / TK;
+  auto fill = [&](int step) {   // every thread commits one group a call, also an empty one, so that the groups count the steps
+    if (step < steps) {
+      const int k0 = step * TK;
+      __nv_bfloat16* a_stage = ring + (size_t)(step % MMA_STAGES) * STAGE_ELEMENTS;
+      __nv_bfloat16* b_stage = a_stage + A_ELEMENTS;
+      for (int x = threadIdx.x; x < EXPERT_ROWS * (TK / 8); x += 128) {
+        const int r = x / (TK / 8), c = (x % (TK / 8)) * 8;
+        const int row = rows[r];
+        const bool real = row >= 0 && k0 + c < k_size;
+        copy_16_or_zeros(a_stage + r * LD + c, real ? a + (long long)row * lda + k0 + c : a, real);
+      }
+      for (int x = threadIdx.x; x < G * TN * (TK / 8); x += 128) {
+        const int g = x / (TN * (TK / 8)), y = x % (TN * (TK / 8));
+        const int r = y / (TK / 8), c = (y % (TK / 8)) * 8;
+        const bool real = n0 + r < n_out && k0 + c < k_size;
+        copy_16_or_zeros(b_stage + (g * TN + r) * LD + c, real ? w_mine + glu_row(n0 + r, g, n_out, GLU && interleaved) * k_size + k0 + c : w_mine, real);
+      }
     }
-    for (int x = threadIdx.x; x < G * TN * (TK / 8); x += 128) {
-      const int g = x / (TN * (TK / 8)), y = x % (TN * (TK / 8));
-      const int r = y / (TK / 8), c = (y % (TK / 8)) * 8;
-      const bool inside = n0 + r < n_out && k0 + c < k_size;
-      *reinterpret_cast<uint4*>(&b_tile[g][r][c]) =
-          inside ? *reinterpret_cast<const uint4*>(w_mine + ((long long)g * n_out + n0 + r) * k_size + k0 + c) : zero;
-    }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+#pragma unroll
+  for (int step = 0; step < MMA_STAGES - 1; ++step) fill(step);
+  for (int step = 0; step < steps; ++step) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(MMA_STAGES - 2) : "memory");   // this step's stage has arrived (for this thread's copies)
+    __syncthreads();                                                               // ... for everyone's; and the stage of the step before is free
+    fill(step + MMA_STAGES - 1);
+    const __nv_bfloat16* a_stage = ring + (size_t)(step % MMA_STAGES) * STAGE_ELEMENTS;
+    const __nv_bfloat16* b_stage = a_stage + A_ELEMENTS;
 #pragma unroll
     for (int kk = 0; kk < TK; kk += 16) {
       unsigned af[2][4];
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
-        af[i][0] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group][kk + 2 * quad]);
-        af[i][1] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group + 8][kk + 2 * quad]);
-        af[i][2] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group][kk + 2 * quad + 8]);
-        af[i][3] = *reinterpret_cast<const unsigned*>(&a_tile[16 * i + group + 8][kk + 2 * quad + 8]);
+        af[i][0] = *reinterpret_cast<const unsigned*>(a_stage + (16 * i + group) * LD + kk + 2 * quad);
+        af[i][1] = *reinterpret_cast<const unsigned*>(a_stage + (16 * i + group + 8) * LD + kk + 2 * quad);
+        af[i][2] = *reinterpret_cast<const unsigned*>(a_stage + (16 * i + group) * LD + kk + 2 * quad + 8);
+        af[i][3] = *reinterpret_cast<const unsigned*>(a_stage + (16 * i + group + 8) * LD + kk + 2 * quad + 8);
       }
 #pragma unroll
       for (int g = 0; g < G; ++g)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int n = 16 * warp + 8 * j + group;
-          const unsigned b0 = *reinterpret_cast<const unsigned*>(&b_tile[g][n][kk + 2 * quad]);
-          const unsigned b1 = *reinterpret_cast<const unsigned*>(&b_tile[g][n][kk + 2 * quad + 8]);
+          const unsigned b0 = *reinterpret_cast<const unsigned*>(b_stage + (g * TN + n) * LD + kk + 2 * quad);
+          const unsigned b1 = *reinterpret_cast<const unsigned*>(b_stage + (g * TN + n) * LD + kk + 2 * quad + 8);
 #pragma unroll
           for (int i = 0; i < 2; ++i)
             asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -280,8 +312,8 @@ __global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfl
                          : "r"(af[i][0]), "r"(af[i][1]), "r"(af[i][2]), "r"(af[i][3]), "r"(b0), "r"(b1));
         }
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -302,8 +334,9 @@ __global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfl
     }
 }
 
-// out[t, c] = sum_k share[t, k] * y[slot_of[t * top + k], c], the choices in their order.
-__global__ void experts_gather_kernel(const float* __restrict__ y, const int* __restrict__ slot_of, const float* __restrict__ share,
+// out[t, c] = sum_k share[t, k] * y[slot_of[t * top + k], c], the choices in their order; y in float32 or in the compute dtype.
+template <typename Y>
+__global__ void experts_gather_kernel(const Y* __restrict__ y, const int* __restrict__ slot_of, const float* __restrict__ share,
                                       float* __restrict__ out, int width, int top, long long total) {
   grid_dependency_wait();
   allow_dependents();
@@ -312,8 +345,22 @@ __global__ void experts_gather_kernel(const float* __restrict__ y, const int* __
   const long long t = item / width;
   const int c = (int)(item % width);
   float acc = 0.f;
-  for (int k = 0; k < top; ++k) acc = fmaf(share[t * top + k], y[(long long)slot_of[t * top + k] * width + c], acc);
+  for (int k = 0; k < top; ++k) acc = fmaf(share[t * top + k], to_float<Y>(y[(long long)slot_of[t * top + k] * width + c]), acc);
   out[item] = acc;
+}
+
+// sorted[slot, :] = h[source[slot] / top, :], zeros in an empty slot: the tokens' rows in the order of their experts, for a product
+// that takes whole row tiles from memory.  A thread moves 16 bytes; chunks = 16-byte pieces of a row.
+__global__ void experts_sort_rows_kernel(const uint4* __restrict__ h, long long ld_chunks, const int* __restrict__ source, uint4* __restrict__ sorted,
+                                         int chunks, int top, long long total) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= total) return;
+  const long long slot = item / chunks;
+  const int c = (int)(item % chunks);
+  const int pair = source[slot];
+  sorted[item] = pair < 0 ? make_uint4(0, 0, 0, 0) : h[(long long)(pair / top) * ld_chunks + c];
 }
 
 }  // namespace pylon
@@ -337,45 +384,81 @@ extern "C" int pylon_experts_route(const void* h, long long ld, const float* rou
   PYLON_CHECK_LAUNCH("experts_route");
 }
 
+// tile_rows: the slots of a row tile (pylon_experts_row_tile() for the products of this file, 128 for the grouped tcgen05 product).
 extern "C" int pylon_experts_plan(const int* chosen, int* slot_of, int* source, int* tile_expert, int pairs, int experts, int max_slots,
-                                  int max_tiles, cudaStream_t stream) {
+                                  int max_tiles, int tile_rows, cudaStream_t stream) {
   if (pairs <= 0) return 0;
-  if (max_slots < pairs || max_tiles * EXPERT_ROWS < max_slots) PYLON_REFUSE("experts_plan: %d slots in %d tiles for %d pairs", max_slots, max_tiles, pairs);
+  if (tile_rows < 1 || max_slots < pairs || (long long)max_tiles * tile_rows < max_slots)
+    PYLON_REFUSE("experts_plan: %d slots in %d tiles of %d for %d pairs", max_slots, max_tiles, tile_rows, pairs);
   launch_dependent(experts_plan_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, chosen, slot_of, source, tile_expert,
-                   pairs, experts, max_slots, max_tiles);
+                   pairs, experts, max_slots, max_tiles, tile_rows);
   PYLON_CHECK_LAUNCH("experts_plan");
 }
 
-// a: [rows, lda] in dtype; w: [experts, (glu ? 2 : 1) * n_out, k] in dtype, contiguous; out: [max_tiles * EXPERT_ROWS, n_out], in dtype with glu, else float32.
+template <bool GLU>
+static void allow_mma_shared_memory() {
+  static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
+  bool& configured = configured_on[pylon::current_device_slot()];
+  if (configured) return;
+  cudaFuncSetAttribute(experts_product_mma_kernel<GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_shared_bytes(GLU));
+  configured = true;
+}
+
+// a: [rows, lda] in dtype; w: [experts, (glu ? 2 : 1) * n_out, k] in dtype, contiguous (with glu an expert's gate rows, then its up rows;
+// or, interleaved != 0, alternating in groups of 8); out: [max_tiles * EXPERT_ROWS, n_out], in dtype with glu, else float32.
 extern "C" int pylon_experts_product(const void* a, long long lda, const void* w, const int* source, const int* tile_expert, int gathered,
-                                     int divide, void* out, int n_out, int k_size, int max_tiles, int glu, int kind, int dtype,
+                                     int divide, void* out, int n_out, int k_size, int max_tiles, int glu, int kind, int interleaved, int dtype,
                                      cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   if (n_out <= 0 || k_size <= 0 || divide < 1 || kind < 0 || kind > 2) PYLON_REFUSE("experts_product: n %d, k %d, divide %d, activation %d", n_out, k_size, divide, kind);
   if (max_tiles > 65535) PYLON_REFUSE("experts_product: %d row tiles", max_tiles);
+  if (interleaved && (!glu || n_out % 8)) PYLON_REFUSE("experts_product: interleaved rows need a gated product of a multiple of 8 columns, got %d", n_out);
   const dim3 grid((unsigned)((n_out + 63) / 64), (unsigned)max_tiles);
   if (dtype == PYLON_DTYPE_F32) {
-    if (glu) launch_dependent(experts_product_kernel<float, true>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
-    else launch_dependent(experts_product_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+    if (glu) launch_dependent(experts_product_kernel<float, true>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+    else launch_dependent(experts_product_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
   } else if (dtype == PYLON_DTYPE_BF16) {
     const __nv_bfloat16* ab = (const __nv_bfloat16*)a;
     const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
     const bool vectors = k_size % 8 == 0 && lda % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)w % 16 == 0;
     if (vectors) {
-      if (glu) launch_dependent(experts_product_mma_kernel<true>, grid, dim3(128), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
-      else launch_dependent(experts_product_mma_kernel<false>, grid, dim3(128), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+      if (glu) {
+        allow_mma_shared_memory<true>();
+        launch_dependent(experts_product_mma_kernel<true>, grid, dim3(128), mma_shared_bytes(true), stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+      } else {
+        allow_mma_shared_memory<false>();
+        launch_dependent(experts_product_mma_kernel<false>, grid, dim3(128), mma_shared_bytes(false), stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+      }
     } else {
-      if (glu) launch_dependent(experts_product_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
-      else launch_dependent(experts_product_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind);
+      if (glu) launch_dependent(experts_product_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+      else launch_dependent(experts_product_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
     }
   } else PYLON_REFUSE("experts_product: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("experts_product");
 }
 
-extern "C" int pylon_experts_gather(const float* y, const int* slot_of, const float* share, float* out, int num_tokens, int width, int top,
+// h [T, ld] and sorted [max_slots, width] in a 16-bit or 32-bit dtype; rows of whole 16-byte pieces at 16-byte addresses.
+extern "C" int pylon_experts_sort_rows(const void* h, long long ld, const int* source, void* sorted, int width, int top, int max_slots, int dtype,
+                                       cudaStream_t stream) {
+  if (max_slots <= 0) return 0;
+  const int per_chunk = dtype == PYLON_DTYPE_F32 ? 4 : 8;
+  if (top < 1 || width % per_chunk || ld % per_chunk || (uintptr_t)h % 16 || (uintptr_t)sorted % 16)
+    PYLON_REFUSE("experts_sort_rows: rows of %d (stride %lld) are not whole 16-byte pieces at 16-byte addresses", width, ld);
+  const int chunks = width / per_chunk;
+  const long long total = (long long)max_slots * chunks;
+  launch_dependent(experts_sort_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const uint4*)h, ld / per_chunk, source, (uint4*)sorted,
+                   chunks, top, total);
+  PYLON_CHECK_LAUNCH("experts_sort_rows");
+}
+
+// y: [slots, width] in float32 (y_dtype PYLON_DTYPE_F32) or bfloat16; out float32 [num_tokens, width].
+extern "C" int pylon_experts_gather(const void* y, const int* slot_of, const float* share, float* out, int num_tokens, int width, int top, int y_dtype,
                                     cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const long long total = (long long)num_tokens * width;
-  launch_dependent(experts_gather_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, slot_of, share, out, width, top, total);
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (y_dtype == PYLON_DTYPE_F32) launch_dependent(experts_gather_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, slot_of, share, out, width, top, total);
+  else if (y_dtype == PYLON_DTYPE_BF16) launch_dependent(experts_gather_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)y, slot_of, share, out, width, top, total);
+  else PYLON_REFUSE("experts_gather: unknown dtype %d", y_dtype);
   PYLON_CHECK_LAUNCH("experts_gather");
 }

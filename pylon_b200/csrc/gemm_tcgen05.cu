@@ -304,7 +304,8 @@ template <int BN, int MODE, int D>
 __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                       const __grid_constant__ CUtensorMap map_b,
                                                                       const __grid_constant__ CUtensorMap map_c, int M, int N, int K,
-                                                                      int* __restrict__ error, const RotateArgs rot) {
+                                                                      int* __restrict__ error, const RotateArgs rot,
+                                                                      const int* __restrict__ tile_group, int group_rows) {
   constexpr bool SWIGLU = MODE == TC_SWIGLU;
   using S = TcShared<BN>;
   constexpr int STAGES = S::STAGES;
@@ -350,13 +351,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
       bool alive = true;
       for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;   // neighbours in the grid share their B tile
+        const int group = tile_group ? tile_group[tile % tiles_m] : 0;
+        if (group < 0) continue;                                               // a row tile that holds nothing: all three roles pass over it
+        const int b_row = group * group_rows + n0;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) { atomicExch(error, 1); alive = false; break; }
           mbar_expect_tx(&full[stage], S::A_BYTES + S::B_BYTES);
           tma_load_2d(a_tiles + (size_t)stage * S::A_BYTES, &map_a, &full[stage], kb * TC_BK, m0);
 #pragma unroll
           for (int piece = 0; piece < S::PIECES; ++piece)
-            tma_load_2d(b_tiles + (size_t)stage * S::B_BYTES + (size_t)piece * S::PIECE_ROWS * 128, &map_b, &full[stage], kb * TC_BK, n0 + piece * S::PIECE_ROWS);
+            tma_load_2d(b_tiles + (size_t)stage * S::B_BYTES + (size_t)piece * S::PIECE_ROWS * 128, &map_b, &full[stage], kb * TC_BK, b_row + piece * S::PIECE_ROWS);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -367,8 +371,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
       uint32_t stage = 0, phase = 0;
       uint32_t round = 0;
       bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++round) {
+      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+        if (tile_group && tile_group[tile % tiles_m] < 0) continue;
         const uint32_t buffer = round % ACCUMULATORS, buffer_phase = (round / ACCUMULATORS) & 1;
+        ++round;
         if (!mbar_wait(&acc_empty[buffer], buffer_phase ^ 1)) { atomicExch(error, 2); break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + buffer * BN;
@@ -395,9 +401,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tcgen05_kernel(const __gri
     unsigned char* my_staging = staging + (size_t)quarter * 2 * 32 * 128;
     const int out_columns = SWIGLU ? N / 2 : N;
     uint32_t round = 0, staged = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      if (tile_group && tile_group[tile % tiles_m] < 0) continue;
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * BN;
       const uint32_t buffer = round % ACCUMULATORS, buffer_phase = (round / ACCUMULATORS) & 1;
+      ++round;
       if (!mbar_wait(&acc_full[buffer], buffer_phase)) { atomicExch(error, 3); break; }
       tc_fence_after();
       const int row0 = m0 + quarter * 32;
@@ -498,7 +506,8 @@ static bool make_map(CUtensorMap* map, const void* base, long long rows, long lo
 
 template <int BN, bool SWIGLU>
 static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __nv_bfloat16* c, int M, int N, int K, long long ldc,
-                          int* error, int sm_count, cudaStream_t stream, float unit_limit = 0.f, float unit_alpha = 1.f) {
+                          int* error, int sm_count, cudaStream_t stream, float unit_limit = 0.f, float unit_alpha = 1.f,
+                          const int* tile_group = nullptr, int group_rows = 0) {
   auto kernel = gemm_tcgen05_kernel<BN, SWIGLU ? TC_SWIGLU : TC_PLAIN, 128>;
   static bool configured_on[pylon::MAX_DEVICES] = {};   // function attributes belong to a device
   bool& configured = configured_on[pylon::current_device_slot()];
@@ -514,7 +523,7 @@ static int launch_tcgen05(const CUtensorMap& map_a, const CUtensorMap& map_b, __
   RotateArgs unit{};
   unit.unit_limit = unit_limit;
   unit.unit_alpha = unit_alpha;
-  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_c, M, N, K, error, unit);
+  launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_c, M, N, K, error, unit, tile_group, group_rows);
   PYLON_CHECK_LAUNCH("gemm_tcgen05");
 }
 
@@ -532,7 +541,7 @@ static int launch_rotate(const CUtensorMap& map_a, const CUtensorMap& map_b, int
   const int tiles = ((M + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
   const int blocks = tiles < sm_count ? tiles : sm_count;
   launch_dependent<LAUNCH_GEMM>(kernel, dim3(blocks), dim3(TC_THREADS), TcShared<BN>::BYTES, stream, map_a, map_b, map_a /* no output map */, M, N, K, error,
-                                rot);
+                                rot, (const int*)nullptr, 0);
   PYLON_CHECK_LAUNCH("gemm_tcgen05_qkv");
 }
 
@@ -551,7 +560,8 @@ extern "C" int pylon_gemm_tcgen05_force_tile(int columns) {
 // swiglu != 0: w's rows alternate in groups of 8 between gate and up rows and y receives silu(gate) * up.
 // error: one int in device memory; the kernel sets it non-zero if one of its waits ran out (the result is then void).
 static int gemm_tcgen05_entry(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
-                             long long ldy, int swiglu, float unit_limit, float unit_alpha, int* error, int sm_count, cudaStream_t stream) {
+                             long long ldy, int swiglu, float unit_limit, float unit_alpha, int* error, int sm_count, cudaStream_t stream,
+                             const int* tile_group = nullptr, int groups = 1) {
   using namespace pylon;
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || ldy % 8) PYLON_REFUSE("gemm_tcgen05: K = %d and the row strides must be multiples of 8", K);
@@ -567,6 +577,7 @@ static int gemm_tcgen05_entry(const void* x, const void* w, void* y, int M, int 
   for (int candidate : {288, 256, 192, 160, 128}) {
     if (forced_columns && candidate != forced_columns) continue;
     if (swiglu && (candidate == 160 || candidate == 288)) continue;   // their accumulator columns do not divide into stores of 32 output columns
+    if (tile_group && (candidate == 160 || candidate == 288)) continue;
     const long long tiles = tiles_m * ((N + candidate - 1) / candidate);
     const long long rounds = (tiles + sm_count - 1) / sm_count;
     // A tile's time is what its operands take to arrive from L2, (128 + width) rows of k a step, plus its start and end:
@@ -576,20 +587,31 @@ static int gemm_tcgen05_entry(const void* x, const void* w, void* y, int M, int 
     if (best < 0 || cost < best) { best = cost; bn = candidate; }
   }
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, x, M, K, ldx, TC_BM) || !make_map(&map_b, w, N, K, ldw, bn > 256 ? bn / 2 : bn))
+  if (!make_map(&map_a, x, M, K, ldx, TC_BM) || !make_map(&map_b, w, (long long)groups * N, K, ldw, bn > 256 ? bn / 2 : bn))
     PYLON_REFUSE("gemm_tcgen05: the tensor maps could not be made");
   __nv_bfloat16* out = (__nv_bfloat16*)y;
 #define PYLON_TC_CASE(BN_)                                                                                          \
   if (bn == BN_) {                                                                                                  \
-    if (swiglu) return launch_tcgen05<BN_, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, unit_limit, unit_alpha); \
-    return launch_tcgen05<BN_, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);                    \
+    if (swiglu) return launch_tcgen05<BN_, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, unit_limit, unit_alpha, tile_group, N); \
+    return launch_tcgen05<BN_, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, 0.f, 1.f, tile_group, N);                          \
   }
   PYLON_TC_CASE(256) PYLON_TC_CASE(192)
 #undef PYLON_TC_CASE
   if (bn == 288) return launch_tcgen05<288, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
   if (bn == 160) return launch_tcgen05<160, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
-  if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, unit_limit, unit_alpha);
-  return launch_tcgen05<128, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream);
+  if (swiglu) return launch_tcgen05<128, true>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, unit_limit, unit_alpha, tile_group, N);
+  return launch_tcgen05<128, false>(map_a, map_b, out, M, N, K, ldy, error, sm_count, stream, 0.f, 1.f, tile_group, N);
+}
+
+// The grouped form: w is [groups, N, K] (contiguous in its first dimension: group g's rows start at row g * N), and the 128 rows of
+// x's row tile i are multiplied by group tile_group[i]'s matrix; a tile whose entry is negative is passed over and its rows of y are
+// left as they are.  tile_group: int32 in device memory, one entry per 128 rows of x.  Where N is not a whole number of tile widths
+// the last tile's operand reaches into the next group's rows (or past the end, which reads zeros); those columns are never stored.
+extern "C" int pylon_gemm_tcgen05_grouped(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,
+                                          long long ldy, int swiglu, const int* tile_group, int groups, int* error, int sm_count,
+                                          cudaStream_t stream) {
+  if (!tile_group || groups < 1) PYLON_REFUSE("gemm_tcgen05_grouped: the row tiles' groups are needed");
+  return gemm_tcgen05_entry(x, w, y, M, N, K, ldx, ldw, ldy, swiglu, 0.f, 1.f, error, sm_count, stream, tile_group, groups);
 }
 
 extern "C" int pylon_gemm_tcgen05_bf16(const void* x, const void* w, void* y, int M, int N, int K, long long ldx, long long ldw,

@@ -204,10 +204,11 @@ _SIGNATURES = {
     "experts.cu": {
         "pylon_experts_row_tile": [],
         "pylon_experts_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "pylon_experts_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_experts_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_experts_product": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_void_p],
-        "pylon_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+                                  c_int, c_void_p],
+        "pylon_experts_sort_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_f32.cu": {
         "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
@@ -247,6 +248,8 @@ _SIGNATURES = {
         "pylon_gemm_tcgen05_glu_clamped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_float, c_float,
                                            c_void_p, c_int, c_void_p],
         "pylon_gemm_tcgen05_force_tile": [c_int],
+        "pylon_gemm_tcgen05_grouped": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int, c_void_p, c_int,
+                                       c_void_p, c_int, c_void_p],
         "pylon_gemm_tcgen05_qkv_rotate": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_float,
                                           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                           c_int, c_void_p, c_void_p, c_int, c_void_p],
@@ -1317,13 +1320,22 @@ def mean_of_normed(outputs: Sequence[torch.Tensor], weights: Sequence[torch.Tens
 # ---------------------------------------------------------------------------------------
 # mixture of experts
 # ---------------------------------------------------------------------------------------
+EXPERT_TILE_ROWS = 128   # the row tile of the grouped tcgen05 product
+
+
 def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[torch.Tensor], w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                   top: int, activation: str = "silu") -> torch.Tensor:
+                   top: int, activation: str = "silu", interleaved: bool = False) -> torch.Tensor:
     """``sum over a token's top experts e of share_e * W_down,e (act(W_gate,e h) * (W_up,e h))`` (``csrc/experts.cu``).
 
     ``h [T, width]``; ``router`` float32 ``[experts, width]`` and ``router_bias`` float32 ``[experts]`` (or None): the logits are
-    float32 whatever ``h`` is; ``w_gate_up [experts, 2 F, width]`` (an expert's gate rows, then its up rows) and ``w_down [experts,
-    width, F]`` in ``h``'s dtype.  Returns float32 ``[1, T, width]`` (the form of partial sums: the residual stream takes it in 32-bit)."""
+    float32 whatever ``h`` is; ``w_gate_up [experts, 2 F, width]`` (an expert's gate rows, then its up rows; with ``interleaved``
+    every expert's rows stacked by :func:`interleave_gate_up`) and ``w_down [experts, width, F]`` in ``h``'s dtype.  Returns float32
+    ``[1, T, width]`` (the form of partial sums: the residual stream takes it in 32-bit).
+
+    The tokens are sorted by expert on the device.  A step of few tokens runs the experts' products from row tiles of 32 slots that
+    gather their rows themselves (``mma.sync``, bound by the matrices coming from memory); a bfloat16 step with about half a
+    128-row tile or more per expert, interleaved weights and ``silu`` copies the rows into their sorted order and runs both
+    products on the grouped form of the tcgen05 kernel (the gated unit in the first one's epilogue)."""
     _need_cuda(h, router, router_bias, w_gate_up, w_down)
     _need(activation in ACTIVATIONS, f"expert_mixture: activation {activation!r}")
     _need(h.dim() == 2 and h.stride(1) == 1, "expert_mixture: h must be [T, width]")
@@ -1334,9 +1346,12 @@ def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[
     _need(router.dtype == torch.float32 and router.shape == (experts, width) and router.is_contiguous(), "expert_mixture: router must be float32 [experts, width]")
     _need(router_bias is None or (router_bias.dtype == torch.float32 and router_bias.shape == (experts,)), "expert_mixture: router_bias must be float32 [experts]")
     _need(1 <= top <= experts, f"expert_mixture: top {top} of {experts} experts")
+    _need(not interleaved or inner % 8 == 0, "expert_mixture: interleaved rows need an inner width that is a multiple of 8")
     library = _library("experts.cu")
-    tile = library.pylon_experts_row_tile()
     pairs = tokens * top
+    grouped = (interleaved and h.dtype == torch.bfloat16 and activation == "silu" and pairs * 2 >= EXPERT_TILE_ROWS * experts and width % 8 == 0
+               and inner % 8 == 0 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0)
+    tile = EXPERT_TILE_ROWS if grouped else library.pylon_experts_row_tile()
     max_tiles = min(pairs, experts) + pairs // tile    # every expert with tokens ends in at most one partly filled tile
     max_slots = max_tiles * tile
     device = h.device
@@ -1348,15 +1363,28 @@ def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[
     code, kind = _dtype_code(h.dtype), ACTIVATIONS[activation]
     _check(library, library.pylon_experts_route(_ptr(h), h.stride(0), _ptr(router), _ptr(router_bias), _ptr(chosen), _ptr(share), width, experts, top,
                                                 tokens, code, _stream()))
-    _check(library, library.pylon_experts_plan(_ptr(chosen), _ptr(slot_of), _ptr(source), _ptr(tile_expert), pairs, experts, max_slots, max_tiles, _stream()))
+    _check(library, library.pylon_experts_plan(_ptr(chosen), _ptr(slot_of), _ptr(source), _ptr(tile_expert), pairs, experts, max_slots, max_tiles, tile, _stream()))
+    out = torch.empty((1, tokens, width), dtype=torch.float32, device=device)
+    if grouped:
+        product = _library("gemm_tcgen05.cu")
+        error, sms = _ptr(tcgen05_error_word(device)), _multiprocessors(device)
+        rows = torch.empty((max_slots, width), dtype=h.dtype, device=device)
+        _check(library, library.pylon_experts_sort_rows(_ptr(h), h.stride(0), _ptr(source), _ptr(rows), width, top, max_slots, code, _stream()))
+        act = torch.empty((max_slots, inner), dtype=h.dtype, device=device)
+        _check(product, product.pylon_gemm_tcgen05_grouped(_ptr(rows), _ptr(w_gate_up), _ptr(act), max_slots, 2 * inner, width, width, width, inner, 1,
+                                                           _ptr(tile_expert), experts, error, sms, _stream()))
+        y = torch.empty((max_slots, width), dtype=h.dtype, device=device)
+        _check(product, product.pylon_gemm_tcgen05_grouped(_ptr(act), _ptr(w_down), _ptr(y), max_slots, width, inner, inner, inner, width, 0,
+                                                           _ptr(tile_expert), experts, error, sms, _stream()))
+        _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, code, _stream()))
+        return out
     act = torch.empty((max_slots, inner), dtype=h.dtype, device=device)
     _check(library, library.pylon_experts_product(_ptr(h), h.stride(0), _ptr(w_gate_up), _ptr(source), _ptr(tile_expert), 1, top, _ptr(act), inner, width,
-                                                  max_tiles, 1, kind, code, _stream()))
+                                                  max_tiles, 1, kind, int(interleaved), code, _stream()))
     y = torch.empty((max_slots, width), dtype=torch.float32, device=device)
     _check(library, library.pylon_experts_product(_ptr(act), inner, _ptr(w_down), _ptr(source), _ptr(tile_expert), 0, 1, _ptr(y), width, inner,
-                                                  max_tiles, 0, kind, code, _stream()))
-    out = torch.empty((1, tokens, width), dtype=torch.float32, device=device)
-    _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, _stream()))
+                                                  max_tiles, 0, kind, 0, code, _stream()))
+    _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, _dtype_code(torch.float32), _stream()))
     return out
 
 

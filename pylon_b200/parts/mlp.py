@@ -135,6 +135,7 @@ class ExpertMixture(FeedForward):
         self.activation, self.router_bias = activation, bool(router_bias)
         self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}.", "gate": "gate", "up": "up", "down": "down", **(names or {})}
         self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+        self.interleaved = False
 
     def _expert(self, index: int, key: str) -> str:
         return self.names["expert"].format(index) + self.names[key]
@@ -150,7 +151,11 @@ class ExpertMixture(FeedForward):
         return decls
 
     def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
-        self.w_gate_up = torch.stack([torch.cat((tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]), dim=0) for e in range(self.experts)]).contiguous()
+        # In bfloat16 with silu an expert's gate and up rows alternate in groups of 8, the layout the tcgen05 product's gated epilogue
+        # takes (the products for few tokens read either layout); otherwise the two halves lie one after the other.
+        self.interleaved = dtype == torch.bfloat16 and self.activation == "silu" and self.intermediate % 8 == 0
+        pair = ops.interleave_gate_up if self.interleaved else (lambda gate, up: torch.cat((gate, up), dim=0))
+        self.w_gate_up = torch.stack([pair(tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]) for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
         self.w_router = tensors[self.names["router"]].contiguous()
         self.b_router = tensors[self.names["router_bias"]].contiguous() if self.router_bias else None
@@ -160,4 +165,4 @@ class ExpertMixture(FeedForward):
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size() + self.w_router.numel() * 4
 
     def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
-        return ops.expert_mixture(h, self.w_router, self.b_router, self.w_gate_up, self.w_down, self.top, self.activation)
+        return ops.expert_mixture(h, self.w_router, self.b_router, self.w_gate_up, self.w_down, self.top, self.activation, self.interleaved)
