@@ -58,8 +58,10 @@ constexpr int MEAN_OF_NORMED_MAX = 4;
 struct NormedInputs { NormedInput of[MEAN_OF_NORMED_MAX]; };
 
 // A block per token.  Per input: the row is added up over its parts, its sum of squares reduced over the block, and the
-// normed row joins the mean.  A row is read twice (once for the root mean square, once for the result).
-template <typename T>
+// normed row joins the mean.  HELD: a thread keeps its (at most MEAN_HELD) columns of every input in registers between the
+// sum of squares and the result, so a row is read once; otherwise it is read twice.
+constexpr int MEAN_HELD = 8;
+template <typename T, bool HELD>
 __global__ void mean_of_normed_kernel(NormedInputs inputs, int count, float* __restrict__ out, int width, long long tokens, float eps) {
   __shared__ float scratch[33];
   grid_dependency_wait();
@@ -76,19 +78,45 @@ __global__ void mean_of_normed_kernel(NormedInputs inputs, int count, float* __r
     }
     return v;
   };
-  for (int i = 0; i < count; ++i) {
-    float sumsq = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      const float v = value(inputs.of[i], c);
-      sumsq = fmaf(v, v, sumsq);
-    }
-    inv[i] = rsqrtf(block_sum(sumsq, scratch) / (float)width + eps);
-  }
   const float share = 1.f / (float)count;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float acc = 0.f;
-    for (int i = 0; i < count; ++i) acc += value(inputs.of[i], c) * inv[i] * inputs.of[i].weight[c];
-    out[t * width + c] = acc * share;
+  if (HELD) {
+    float held[MEAN_OF_NORMED_MAX][MEAN_HELD];
+#pragma unroll
+    for (int i = 0; i < MEAN_OF_NORMED_MAX; ++i) {
+      if (i >= count) break;
+      float sumsq = 0.f;
+#pragma unroll
+      for (int k = 0; k < MEAN_HELD; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        held[i][k] = c < width ? value(inputs.of[i], c) : 0.f;
+        sumsq = fmaf(held[i][k], held[i][k], sumsq);
+      }
+      inv[i] = rsqrtf(block_sum(sumsq, scratch) / (float)width + eps);
+    }
+#pragma unroll
+    for (int k = 0; k < MEAN_HELD; ++k) {
+      const int c = threadIdx.x + k * blockDim.x;
+      if (c >= width) break;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < MEAN_OF_NORMED_MAX; ++i)
+        if (i < count) acc += held[i][k] * inv[i] * inputs.of[i].weight[c];
+      out[t * width + c] = acc * share;
+    }
+  } else {
+    for (int i = 0; i < count; ++i) {
+      float sumsq = 0.f;
+      for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = value(inputs.of[i], c);
+        sumsq = fmaf(v, v, sumsq);
+      }
+      inv[i] = rsqrtf(block_sum(sumsq, scratch) / (float)width + eps);
+    }
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      float acc = 0.f;
+      for (int i = 0; i < count; ++i) acc += value(inputs.of[i], c) * inv[i] * inputs.of[i].weight[c];
+      out[t * width + c] = acc * share;
+    }
   }
 }
 
@@ -135,10 +163,14 @@ extern "C" int pylon_mean_of_normed(const void* const* data, const float* const*
   if (count < 1 || count > MEAN_OF_NORMED_MAX || width <= 0) PYLON_REFUSE("mean_of_normed: %d inputs (1 to %d), width %d", count, MEAN_OF_NORMED_MAX, width);
   NormedInputs inputs;
   for (int i = 0; i < count; ++i) inputs.of[i] = NormedInput{data[i], weights[i], parts[i], is_float[i]};
-  const int threads = width >= 2048 ? 256 : 128;
-  if (dtype == PYLON_DTYPE_F32) launch_dependent(mean_of_normed_kernel<float>, dim3((unsigned)tokens), dim3(threads), 0, stream, inputs, count, out, width, (long long)tokens, eps);
-  else if (dtype == PYLON_DTYPE_BF16)
-    launch_dependent(mean_of_normed_kernel<__nv_bfloat16>, dim3((unsigned)tokens), dim3(threads), 0, stream, inputs, count, out, width, (long long)tokens, eps);
+  // as many threads as leave each at most MEAN_HELD columns (by the width alone, so that a token's sums do not depend on the step)
+  int threads = 128;
+  while (threads < 1024 && threads * MEAN_HELD < width) threads *= 2;
+  const bool held = threads * MEAN_HELD >= width;
+#define PYLON_MEAN(T, HELD) launch_dependent(mean_of_normed_kernel<T, HELD>, dim3((unsigned)tokens), dim3(threads), 0, stream, inputs, count, out, width, (long long)tokens, eps)
+  if (dtype == PYLON_DTYPE_F32) { if (held) PYLON_MEAN(float, true); else PYLON_MEAN(float, false); }
+  else if (dtype == PYLON_DTYPE_BF16) { if (held) PYLON_MEAN(__nv_bfloat16, true); else PYLON_MEAN(__nv_bfloat16, false); }
   else PYLON_REFUSE("mean_of_normed: unknown dtype %d", dtype);
+#undef PYLON_MEAN
   PYLON_CHECK_LAUNCH("mean_of_normed");
 }

@@ -9,7 +9,7 @@
 // padded to whole tiles, and the grouped products run over the most tiles there can be; a tile beyond the last one, and
 // a slot of padding inside a tile, is skipped.
 //
-//   experts_route     a warp per token: router logits, the top choices, their shares
+//   experts_route     router logits, the top choices, their shares: a block per token in a step of few tokens, else a warp per four
 //   experts_plan      one block: tokens per expert, the experts' first tiles, a slot for every pair
 //   experts_product   a block per (row tile, column tile): rows gathered by slot, the expert's matrix, float32 sums in a
 //                     fixed order of k; with GLU the gate and up tiles side by side and act(gate) * up written
@@ -35,37 +35,9 @@ __device__ __forceinline__ long long glu_row(int n, int half, int n_out, int int
   return interleaved ? ((long long)(n >> 3) << 4) + (half << 3) + (n & 7) : (long long)half * n_out + n;
 }
 
-// h [T, width] in T; router float32 [experts, width]; bias float32 [experts] or null.  chosen int32 [T, top], share float32 [T, top].
-// Shared memory: warps * experts floats.
-template <typename T>
-__global__ void experts_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router, const float* __restrict__ bias,
-                                     int* __restrict__ chosen, float* __restrict__ share, int width, int experts, int top, int num_tokens) {
-  extern __shared__ float logits_all[];
-  grid_dependency_wait();
-  allow_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= num_tokens) return;
-  float* logits = logits_all + warp * experts;
-  const T* mine = h + (long long)t * ld;
-  constexpr int SIDE = 8;   // experts side by side: the token's row is read once per eight experts
-  for (int e0 = 0; e0 < experts; e0 += SIDE) {
-    float acc[SIDE];
-#pragma unroll
-    for (int j = 0; j < SIDE; ++j) acc[j] = 0.f;
-    for (int c = lane; c < width; c += 32) {
-      const float x = to_float<T>(mine[c]);
-#pragma unroll
-      for (int j = 0; j < SIDE; ++j)
-        if (e0 + j < experts) acc[j] = fmaf(x, router[(long long)(e0 + j) * width + c], acc[j]);
-    }
-#pragma unroll
-    for (int j = 0; j < SIDE; ++j) {
-      const float z = warp_sum(acc[j]);
-      if (lane == 0 && e0 + j < experts) logits[e0 + j] = z + (bias != nullptr ? bias[e0 + j] : 0.f);
-    }
-  }
-  __syncwarp();
+// The `top` largest of a token's logits (the lower index wins a tie) and the softmax over just those; one warp.  logits is spoilt.
+__device__ __forceinline__ void route_choose(float* logits, int* __restrict__ chosen, float* __restrict__ share, long long t, int experts, int top,
+                                             int lane) {
   float first = 0.f, total = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -84,15 +56,108 @@ __global__ void experts_route_kernel(const T* __restrict__ h, long long ld, cons
     const float weight = expf(best - first);
     total += weight;
     if (lane == 0) {
-      chosen[(long long)t * top + k] = where;
-      share[(long long)t * top + k] = weight;
+      chosen[t * top + k] = where;
+      share[t * top + k] = weight;
       logits[where] = -INFINITY;
     }
     __syncwarp();
   }
   const float inv = 1.f / total;
-  if (lane < top) share[(long long)t * top + lane] *= inv;
-  for (int k = 32 + lane; k < top; k += 32) share[(long long)t * top + k] *= inv;
+  if (lane < top) share[t * top + lane] *= inv;
+  for (int k = 32 + lane; k < top; k += 32) share[t * top + k] *= inv;
+}
+
+// h [T, width] in T; router float32 [experts, width]; bias float32 [experts] or null.  chosen int32 [T, top], share float32 [T, top].
+// A logit is summed in one order whatever the kernel form: the columns fall into four classes by (c mod 128) / 32; within class k
+// lane l adds the columns 128 i + 32 k + l in order of i, the 32 lanes' sums are added up by the same butterfly, and the four class
+// sums are added in order of k.  So a token's choice does not depend on how many tokens the step has.
+//
+// Many tokens: a warp takes TOKENS tokens side by side, so that a router value it has loaded serves all of them, and walks the four
+// classes one after the other.  Shared memory: warps * TOKENS * experts floats.
+template <typename T, int TOKENS>
+__global__ void experts_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router, const float* __restrict__ bias,
+                                     int* __restrict__ chosen, float* __restrict__ share, int width, int experts, int top, int num_tokens) {
+  extern __shared__ float logits_all[];
+  grid_dependency_wait();
+  allow_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = (blockIdx.x * (blockDim.x >> 5) + warp) * TOKENS;
+  if (t0 >= num_tokens) return;
+  constexpr int SIDE = 8;   // experts side by side: the tokens' rows are read once per eight experts
+  for (int e0 = 0; e0 < experts; e0 += SIDE) {
+    float total[TOKENS][SIDE];
+    for (int k = 0; k < 4; ++k) {
+      float acc[TOKENS][SIDE];
+#pragma unroll
+      for (int i = 0; i < TOKENS; ++i)
+#pragma unroll
+        for (int j = 0; j < SIDE; ++j) acc[i][j] = 0.f;
+#pragma unroll 4
+      for (int c = 32 * k + lane; c < width; c += 128) {   // unrolled, so that several columns' loads are on their way at once
+        float x[TOKENS], r[SIDE];
+#pragma unroll
+        for (int i = 0; i < TOKENS; ++i) x[i] = t0 + i < num_tokens ? to_float<T>(h[(long long)(t0 + i) * ld + c]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < SIDE; ++j) r[j] = e0 + j < experts ? router[(long long)(e0 + j) * width + c] : 0.f;
+#pragma unroll
+        for (int i = 0; i < TOKENS; ++i)
+#pragma unroll
+          for (int j = 0; j < SIDE; ++j) acc[i][j] = fmaf(x[i], r[j], acc[i][j]);
+      }
+#pragma unroll
+      for (int i = 0; i < TOKENS; ++i)
+#pragma unroll
+        for (int j = 0; j < SIDE; ++j) {
+          const float z = warp_sum(acc[i][j]);
+          total[i][j] = k == 0 ? z : total[i][j] + z;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TOKENS; ++i)
+#pragma unroll
+      for (int j = 0; j < SIDE; ++j)
+        if (lane == 0 && e0 + j < experts) logits_all[(warp * TOKENS + i) * experts + e0 + j] = total[i][j] + (bias != nullptr ? bias[e0 + j] : 0.f);
+  }
+  __syncwarp();
+  for (int i = 0; i < TOKENS && t0 + i < num_tokens; ++i) route_choose(logits_all + (warp * TOKENS + i) * experts, chosen, share, t0 + i, experts, top, lane);
+}
+
+// Few tokens: a block of four warps per token, warp k takes class k.  Shared memory: (4 * 8 + experts) floats.
+template <typename T>
+__global__ void __launch_bounds__(128) experts_route_block_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router,
+                                                                  const float* __restrict__ bias, int* __restrict__ chosen, float* __restrict__ share,
+                                                                  int width, int experts, int top) {
+  extern __shared__ float route_shared[];
+  constexpr int SIDE = 8;
+  float* parts = route_shared;               // [4][SIDE]
+  float* logits = route_shared + 4 * SIDE;   // [experts]
+  grid_dependency_wait();
+  allow_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t = blockIdx.x;
+  for (int e0 = 0; e0 < experts; e0 += SIDE) {
+    float acc[SIDE];
+#pragma unroll
+    for (int j = 0; j < SIDE; ++j) acc[j] = 0.f;
+#pragma unroll 4
+    for (int c = threadIdx.x; c < width; c += 128) {
+      const float x = to_float<T>(h[t * ld + c]);
+#pragma unroll
+      for (int j = 0; j < SIDE; ++j) acc[j] = fmaf(x, e0 + j < experts ? router[(long long)(e0 + j) * width + c] : 0.f, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < SIDE; ++j) {
+      const float z = warp_sum(acc[j]);
+      if (lane == 0) parts[warp * SIDE + j] = z;
+    }
+    __syncthreads();
+    if (threadIdx.x < SIDE && e0 + threadIdx.x < experts) {
+      const int j = threadIdx.x;
+      logits[e0 + j] = ((parts[j] + parts[SIDE + j]) + parts[2 * SIDE + j]) + parts[3 * SIDE + j] + (bias != nullptr ? bias[e0 + j] : 0.f);
+    }
+    __syncthreads();
+  }
+  if (warp == 0) route_choose(logits, chosen, share, t, experts, top, lane);
 }
 
 // One block.  chosen [pairs]; slot_of [pairs] out; source [max_slots] out: the pair in a slot, or -1; tile_expert [max_tiles] out:
@@ -373,14 +438,23 @@ extern "C" int pylon_experts_route(const void* h, long long ld, const float* rou
                                    int experts, int top, int num_tokens, int dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > experts || experts > 2048) PYLON_REFUSE("experts_route: %d of %d experts (at most 2048)", top, experts);
-  const int warps = 4;
-  const dim3 grid((unsigned)((num_tokens + warps - 1) / warps));
-  const size_t smem = (size_t)warps * experts * sizeof(float);
-  if (dtype == PYLON_DTYPE_F32)
-    launch_dependent(experts_route_kernel<float>, grid, dim3(warps * 32), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
-  else if (dtype == PYLON_DTYPE_BF16)
-    launch_dependent(experts_route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
-  else PYLON_REFUSE("experts_route: unknown dtype %d", dtype);
+  if (num_tokens < 512) {   // a step of few tokens wants many threads a token
+    const size_t smem = (size_t)(4 * 8 + experts) * sizeof(float);
+    if (dtype == PYLON_DTYPE_F32)
+      launch_dependent(experts_route_block_kernel<float>, dim3((unsigned)num_tokens), dim3(128), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top);
+    else if (dtype == PYLON_DTYPE_BF16)
+      launch_dependent(experts_route_block_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(128), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top);
+    else PYLON_REFUSE("experts_route: unknown dtype %d", dtype);
+  } else {
+    const int warps = 4, side = 4;   // tokens a warp takes side by side
+    const dim3 grid((unsigned)((num_tokens + warps * side - 1) / (warps * side)));
+    const size_t smem = (size_t)warps * side * experts * sizeof(float);
+    if (dtype == PYLON_DTYPE_F32)
+      launch_dependent(experts_route_kernel<float, side>, grid, dim3(warps * 32), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
+    else if (dtype == PYLON_DTYPE_BF16)
+      launch_dependent(experts_route_kernel<__nv_bfloat16, side>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
+    else PYLON_REFUSE("experts_route: unknown dtype %d", dtype);
+  }
   PYLON_CHECK_LAUNCH("experts_route");
 }
 

@@ -99,16 +99,22 @@ __device__ __forceinline__ void ssm_copy_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void ssm_copy_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
-// grid (slices of vdim, heads, rows); block = cols columns x P lanes (padded to a whole warp).  PER >= ceil(N / P).  A lane holds
-// the entries p, p + P, ... of its column.  The tokens' B, C, the block's x, decay and step come into shared memory
-// `stage_tokens` tokens at a time by asynchronous copies, two stages in turn.  Shared memory: 2 * stage_tokens * per_token floats,
-// per_token = 2 N + cols + 2 rounded up to a multiple of 4.  `wide`: N, cols and the buffers' addresses allow 16-byte copies.
+// grid (slices of vdim, heads, rows); block = cols columns x P lanes (padded to a whole warp).  PER >= ceil(N / P), a multiple of 4.
+// A lane holds PER neighbouring entries of its column: p * PER, p * PER + 1, ...  The tokens' B, C, the block's x, decay and step
+// come into shared memory `stage_tokens` tokens at a time by asynchronous copies, two stages in turn.  In a stage a token's B (and C)
+// lies lane by lane, PER entries and 4 floats of padding each, so that a lane reads its entries as 16-byte words and the eight lanes
+// that read in one go do not meet in a bank (four entries need no padding); entries past N are zeros, written once.  Shared memory: 2 * stage_tokens * per_token
+// floats, per_token = 2 P ssm_lane_floats(PER) + cols + 2 rounded up to a multiple of 4.  `wide`: N, cols and the buffers' addresses allow
+// 16-byte copies.
+__host__ __device__ constexpr int ssm_lane_floats(int per) { return per == 4 ? 4 : per + 4; }
+
 template <int PER>
 __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float* __restrict__ gates, float* __restrict__ state,
                                       long long slot_floats, const int* __restrict__ q_start, const int* __restrict__ slots,
                                       const float* __restrict__ skip, float* __restrict__ out, int heads, int groups, int n_state, int vdim,
                                       int lanes, int cols, int stage_tokens, int wide) {
   extern __shared__ __align__(16) float stages[];
+  constexpr int LANE_FLOATS = ssm_lane_floats(PER);
   grid_dependency_wait();
   allow_dependents();
   const int P = lanes;
@@ -122,31 +128,37 @@ __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float
   const int group = head / (heads / groups);
   const int inner = heads * vdim, channels = inner + 2 * groups * n_state;
   const int x_col = head * vdim + blockIdx.x * cols, b_col = inner + group * n_state, c_col = inner + groups * n_state + group * n_state;
-  const int per_token = (2 * n_state + cols + 2 + 3) & ~3;   // B | C | the block's x | decay | step | padding
+  const int c_at = P * LANE_FLOATS, x_at = 2 * c_at, gate_at = x_at + cols;   // where C, x and the two gates lie in a token's stage
+  const int per_token = (gate_at + 2 + 3) & ~3;
   float* mine = state + (long long)slots[row] * slot_floats + ((long long)head * n_state) * vdim + j;   // S[n, j] at mine[n * vdim]
   const float d_skip = skip[head];
   float s[PER];
 #pragma unroll
   for (int n = 0; n < PER; ++n) {
-    const int i = p + n * P;
+    const int i = p * PER + n;
     s[n] = (live && i < n_state) ? mine[(long long)i * vdim] : 0.f;
   }
+  if (P * PER > n_state) {   // the entries past N are zeros and stay so: no copy writes them
+    for (int x = threadIdx.x; x < 2 * stage_tokens * per_token; x += blockDim.x) stages[x] = 0.f;
+    __syncthreads();
+  }
+  auto place = [&](int e) { return (e / PER) * LANE_FLOATS + e % PER; };   // where entry e of B or C lies
   auto fetch = [&](int first, int buffer) {
     const int count = min(stage_tokens, end - first);
     if (wide) {
       const int units = (2 * n_state + cols) >> 2;
       for (int x = threadIdx.x; x < count * units; x += blockDim.x) {
         const int token = x / units, e = (x - token * units) << 2;
-        float* dst = stages + ((long long)buffer * stage_tokens + token) * per_token + e;
+        float* dst = stages + ((long long)buffer * stage_tokens + token) * per_token;
         const float* src = xbc + (long long)(first + token) * channels;
-        if (e < n_state) ssm_copy_async_16(dst, src + b_col + e);
-        else if (e < 2 * n_state) ssm_copy_async_16(dst, src + c_col + (e - n_state));
-        else if (blockIdx.x * cols + (e - 2 * n_state) < vdim) ssm_copy_async_16(dst, src + x_col + (e - 2 * n_state));   // vdim is a multiple of 4 here
-        else dst[0] = dst[1] = dst[2] = dst[3] = 0.f;
+        if (e < n_state) ssm_copy_async_16(dst + place(e), src + b_col + e);
+        else if (e < 2 * n_state) ssm_copy_async_16(dst + c_at + place(e - n_state), src + c_col + (e - n_state));
+        else if (blockIdx.x * cols + (e - 2 * n_state) < vdim) ssm_copy_async_16(dst + x_at + (e - 2 * n_state), src + x_col + (e - 2 * n_state));   // vdim is a multiple of 4 here
+        else { float* z = dst + x_at + (e - 2 * n_state); z[0] = z[1] = z[2] = z[3] = 0.f; }
       }
       for (int x = threadIdx.x; x < count * 2; x += blockDim.x) {
         const int token = x >> 1;
-        ssm_copy_async(stages + ((long long)buffer * stage_tokens + token) * per_token + 2 * n_state + cols + (x & 1),
+        ssm_copy_async(stages + ((long long)buffer * stage_tokens + token) * per_token + gate_at + (x & 1),
                        gates + (long long)(first + token) * 2 * heads + ((x & 1) ? heads + head : head));
       }
       ssm_copy_commit();
@@ -157,12 +169,12 @@ __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float
       const float* src = xbc + (long long)(first + token) * channels;
       const float* gate = gates + (long long)(first + token) * 2 * heads;
       for (int e = threadIdx.x; e < 2 * n_state + cols + 2; e += blockDim.x) {
-        if (e < n_state) ssm_copy_async(dst + e, src + b_col + e);
-        else if (e < 2 * n_state) ssm_copy_async(dst + e, src + c_col + (e - n_state));
+        if (e < n_state) ssm_copy_async(dst + place(e), src + b_col + e);
+        else if (e < 2 * n_state) ssm_copy_async(dst + c_at + place(e - n_state), src + c_col + (e - n_state));
         else if (e < 2 * n_state + cols) {
           const int c = e - 2 * n_state;
-          if (blockIdx.x * cols + c < vdim) ssm_copy_async(dst + e, src + x_col + c); else dst[e] = 0.f;
-        } else ssm_copy_async(dst + e, gate + (e == 2 * n_state + cols ? head : heads + head));
+          if (blockIdx.x * cols + c < vdim) ssm_copy_async(dst + x_at + c, src + x_col + c); else dst[x_at + c] = 0.f;
+        } else ssm_copy_async(dst + gate_at + (e - 2 * n_state - cols), gate + (e == 2 * n_state + cols ? head : heads + head));
       }
     }
     ssm_copy_commit();
@@ -179,23 +191,31 @@ __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float
     __syncthreads();
     const int count = min(stage_tokens, end - first);
     const float* staged = stages + (long long)buffer * stage_tokens * per_token;
+    float* y_at = out + ((long long)first * heads + head) * vdim + j;
 #pragma unroll 2
     for (int token = 0; token < count; ++token) {
       const float* here = staged + token * per_token;
-      const float x = column < cols ? here[2 * n_state + column] : 0.f;
-      const float a = here[2 * n_state + cols], dt = here[2 * n_state + cols + 1];
+      const float x = column < cols ? here[x_at + column] : 0.f;
+      const float a = here[gate_at], dt = here[gate_at + 1];
       const float write = dt * x;
+      const float4* b4 = reinterpret_cast<const float4*>(here + p * LANE_FLOATS);
+      const float4* c4 = reinterpret_cast<const float4*>(here + c_at + p * LANE_FLOATS);
       float read[2] = {0.f, 0.f};
 #pragma unroll
-      for (int n = 0; n < PER; ++n) {
-        const int i = p + n * P;
-        const float b = i < n_state ? here[i] : 0.f, c = i < n_state ? here[n_state + i] : 0.f;
-        s[n] = fmaf(s[n], a, b * write);
-        read[n & 1] = fmaf(s[n], c, read[n & 1]);
+      for (int n = 0; n < PER; n += 4) {
+        const float4 b = b4[n >> 2], c = c4[n >> 2];
+        s[n] = fmaf(s[n], a, b.x * write);
+        s[n + 1] = fmaf(s[n + 1], a, b.y * write);
+        s[n + 2] = fmaf(s[n + 2], a, b.z * write);
+        s[n + 3] = fmaf(s[n + 3], a, b.w * write);
+        read[0] = fmaf(s[n], c.x, read[0]);
+        read[1] = fmaf(s[n + 1], c.y, read[1]);
+        read[0] = fmaf(s[n + 2], c.z, read[0]);
+        read[1] = fmaf(s[n + 3], c.w, read[1]);
       }
       float y = read[0] + read[1];
       for (int offset = P >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
-      if (live && p == 0) out[((long long)(first + token) * heads + head) * vdim + j] = fmaf(d_skip, x, y);
+      if (live && p == 0) y_at[(long long)token * heads * vdim] = fmaf(d_skip, x, y);
     }
     __syncthreads();   // the stage is free to be filled again
     buffer ^= 1;
@@ -203,7 +223,7 @@ __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float
   if (live) {
 #pragma unroll
     for (int n = 0; n < PER; ++n) {
-      const int i = p + n * P;
+      const int i = p * PER + n;
       if (i < n_state) mine[(long long)i * vdim] = s[n];
     }
   }
@@ -261,7 +281,9 @@ static int launch_state_space(const void* proj_v, long long ld, const float* con
                      col_conv, taps, state, slot_floats, conv_offset, q_start, slots, channels, num_rows);
   }
   {
-    // P lanes share a column: the fewest (a power of two) that leave a lane at most 16 entries
+    // P lanes share a column: the fewest (a power of two) that leave a lane at most 16 entries.  (More lanes with fewer entries
+    // each put more warps on a scheduler, but a warp's work per token is mostly what does not shrink with its entries - staging,
+    // shuffles, the store - so 32 lanes of 4 entries took as long as 8 lanes of 16 at 32 heads of 128 x 64.)
     int lanes = 1;
     while (lanes < 32 && (n_state + lanes - 1) / lanes > 16) lanes *= 2;
     const int per = (n_state + lanes - 1) / lanes;
@@ -269,7 +291,8 @@ static int launch_state_space(const void* proj_v, long long ld, const float* con
     while (cols > 1 && cols / 2 >= vdim) cols /= 2;
     dim3 grid((vdim + cols - 1) / cols, heads, num_rows);
     const int threads = cols * lanes;
-    const int per_token = (2 * n_state + cols + 2 + 3) & ~3;
+    const int per_slot = per <= 4 ? 4 : per <= 8 ? 8 : per <= 16 ? 16 : 32;   // the kernel's PER
+    const int per_token = (2 * lanes * ssm_lane_floats(per_slot) + cols + 2 + 3) & ~3;
     const int wide = n_state % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && (uintptr_t)xbc % 16 == 0;
     int stage_tokens = 16;
     while (stage_tokens > 1 && 2LL * stage_tokens * per_token * (long long)sizeof(float) > 48 * 1024) stage_tokens /= 2;
