@@ -277,12 +277,13 @@ __global__ void __launch_bounds__(256) experts_product_kernel(const T* __restric
 
 // The same product on tensor cores for bfloat16: a block of four warps takes a row tile of 32 slots x 64 columns (with GLU: 64 gate and
 // the 64 matching up columns); warp w owns columns 16 w .. 16 w + 15 of the tile, both 16-row halves.  Steps of 64 along k through a ring
-// of MMA_STAGES shared-memory stages that cp.async fills ahead of the products (a step of few tokens is bound by the experts' matrices
+// of four shared-memory stages that cp.async fills ahead of the products (a step of few tokens is bound by the experts' matrices
 // coming from memory, so several steps' loads are kept in flight); rows padded by 8 elements so that fragment loads do not collide;
 // k_size is a multiple of 8, the rest of a step and the rows of empty slots are filled with zeros.
-constexpr int MMA_TN = 64, MMA_TK = 64, MMA_PAD = 8, MMA_STAGES = 4;
+constexpr int MMA_TN = 64, MMA_TK = 64, MMA_PAD = 8;
+__host__ __device__ constexpr int mma_stages(bool) { return 4; }   // (six stages for the plain product, whose stages are half as large, were faster at width 2,048 and slower at 4,096)
 __host__ __device__ constexpr int mma_stage_elements(bool glu) { return (EXPERT_ROWS + (glu ? 2 : 1) * MMA_TN) * (MMA_TK + MMA_PAD); }
-constexpr size_t mma_shared_bytes(bool glu) { return (size_t)MMA_STAGES * mma_stage_elements(glu) * sizeof(__nv_bfloat16); }
+constexpr size_t mma_shared_bytes(bool glu) { return (size_t)mma_stages(glu) * mma_stage_elements(glu) * sizeof(__nv_bfloat16); }
 
 __device__ __forceinline__ void copy_16_or_zeros(void* shared, const void* global, bool real) {
   const unsigned target = (unsigned)__cvta_generic_to_shared(shared);
@@ -295,7 +296,7 @@ __global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfl
                                                                   const __nv_bfloat16* __restrict__ w, const int* __restrict__ source,
                                                                   const int* __restrict__ tile_expert, int gathered, int divide,
                                                                   void* __restrict__ out_v, int n_out, int k_size, int kind, int interleaved) {
-  constexpr int TN = MMA_TN, TK = MMA_TK, LD = MMA_TK + MMA_PAD, G = GLU ? 2 : 1;
+  constexpr int TN = MMA_TN, TK = MMA_TK, LD = MMA_TK + MMA_PAD, G = GLU ? 2 : 1, MMA_STAGES = mma_stages(GLU);
   constexpr int A_ELEMENTS = EXPERT_ROWS * LD, STAGE_ELEMENTS = mma_stage_elements(GLU);
   extern __shared__ __align__(16) unsigned char mma_shared[];
   __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(mma_shared);
