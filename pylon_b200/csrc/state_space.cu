@@ -108,16 +108,15 @@ __device__ __forceinline__ void ssm_copy_wait() { asm volatile("cp.async.wait_gr
 // 16-byte copies.
 __host__ __device__ constexpr int ssm_lane_floats(int per) { return per == 4 ? 4 : per + 4; }
 
-template <int PER>
+template <int PER, int P>
 __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float* __restrict__ gates, float* __restrict__ state,
                                       long long slot_floats, const int* __restrict__ q_start, const int* __restrict__ slots,
                                       const float* __restrict__ skip, float* __restrict__ out, int heads, int groups, int n_state, int vdim,
-                                      int lanes, int cols, int stage_tokens, int wide) {
+                                      int cols, int stage_tokens, int wide) {
   extern __shared__ __align__(16) float stages[];
   constexpr int LANE_FLOATS = ssm_lane_floats(PER);
   grid_dependency_wait();
   allow_dependents();
-  const int P = lanes;
   const int p = threadIdx.x % P;
   const int column = threadIdx.x / P;
   const int j = blockIdx.x * cols + column;
@@ -192,7 +191,7 @@ __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float
     const int count = min(stage_tokens, end - first);
     const float* staged = stages + (long long)buffer * stage_tokens * per_token;
     float* y_at = out + ((long long)first * heads + head) * vdim + j;
-#pragma unroll 2
+#pragma unroll 4
     for (int token = 0; token < count; ++token) {
       const float* here = staged + token * per_token;
       const float x = column < cols ? here[x_at + column] : 0.f;
@@ -214,6 +213,7 @@ __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float
         read[1] = fmaf(s[n + 3], c.w, read[1]);
       }
       float y = read[0] + read[1];
+#pragma unroll
       for (int offset = P >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
       if (live && p == 0) y_at[(long long)token * heads * vdim] = fmaf(d_skip, x, y);
     }
@@ -291,18 +291,22 @@ static int launch_state_space(const void* proj_v, long long ld, const float* con
     while (cols > 1 && cols / 2 >= vdim) cols /= 2;
     dim3 grid((vdim + cols - 1) / cols, heads, num_rows);
     const int threads = cols * lanes;
-    const int per_slot = per <= 4 ? 4 : per <= 8 ? 8 : per <= 16 ? 16 : 32;   // the kernel's PER
+    const int per_slot = lanes > 1 ? (per <= 16 ? 16 : 32) : per <= 4 ? 4 : per <= 8 ? 8 : 16;   // the kernel's PER
     const int per_token = (2 * lanes * ssm_lane_floats(per_slot) + cols + 2 + 3) & ~3;
     const int wide = n_state % 4 == 0 && vdim % 4 == 0 && cols % 4 == 0 && (uintptr_t)xbc % 16 == 0;
     int stage_tokens = 16;
     while (stage_tokens > 1 && 2LL * stage_tokens * per_token * (long long)sizeof(float) > 48 * 1024) stage_tokens /= 2;
     const size_t smem = 2ull * stage_tokens * per_token * sizeof(float);
-#define PYLON_SSM_RECURRENCE(N) \
-    launch_dependent(ssm_recurrence_kernel<N>, grid, dim3(threads < 32 ? 32 : threads), smem, stream, xbc, gates, state, slot_floats, q_start, slots, skip, y, heads, groups, n_state, vdim, lanes, cols, stage_tokens, wide)
-    if (per <= 4) PYLON_SSM_RECURRENCE(4);
-    else if (per <= 8) PYLON_SSM_RECURRENCE(8);
-    else if (per <= 16) PYLON_SSM_RECURRENCE(16);
-    else PYLON_SSM_RECURRENCE(32);
+#define PYLON_SSM_RECURRENCE(N, L) \
+    launch_dependent(ssm_recurrence_kernel<N, L>, grid, dim3(threads < 32 ? 32 : threads), smem, stream, xbc, gates, state, slot_floats, q_start, slots, skip, y, heads, groups, n_state, vdim, cols, stage_tokens, wide)
+    // the lanes and entries that the rule above can give: one lane up to 16 entries, then 16 entries up to 32 lanes, then 32 entries
+    if (lanes == 1) { if (per <= 4) PYLON_SSM_RECURRENCE(4, 1); else if (per <= 8) PYLON_SSM_RECURRENCE(8, 1); else PYLON_SSM_RECURRENCE(16, 1); }
+    else if (lanes == 2) PYLON_SSM_RECURRENCE(16, 2);
+    else if (lanes == 4) PYLON_SSM_RECURRENCE(16, 4);
+    else if (lanes == 8) PYLON_SSM_RECURRENCE(16, 8);
+    else if (lanes == 16) PYLON_SSM_RECURRENCE(16, 16);
+    else if (per <= 16) PYLON_SSM_RECURRENCE(16, 32);
+    else PYLON_SSM_RECURRENCE(32, 32);
 #undef PYLON_SSM_RECURRENCE
   }
   launch_dependent(ssm_gated_norm_kernel<T>, dim3((unsigned)num_tokens * norm_groups), dim3(128), 0, stream, y, proj, ld, 0, norm_weight,

@@ -612,7 +612,7 @@ def test_the_gated_unit_with_relu_and_biases(width, ff, tokens, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("width,ff,experts,top,tokens", [(40, 12, 3, 1, 1), (56, 20, 5, 5, 7), (48, 24, 10, 4, 150), (256, 128, 6, 2, 200), (128, 64, 33, 3, 70),
-                                                          (64, 40, 2, 1, 40), (256, 136, 4, 2, 700), (320, 256, 3, 1, 600), (128, 520, 5, 3, 333)])
+                                                          (64, 40, 2, 1, 40), (256, 136, 4, 2, 700), (384, 256, 3, 1, 600), (128, 520, 5, 3, 333)])
 def test_the_mixture_of_experts_against_token_by_token(width, ff, experts, top, tokens, dtype):
     """Router logits in 32-bit with a bias, the largest ``top``, the softmax over just those, the chosen experts' gated units:
     one token, few and many, fewer tokens than experts and more, every expert used, tiles that are partly filled; the last shapes
