@@ -146,6 +146,80 @@ __global__ void mean_of_normed_kernel(NormedInputs inputs, int count, float* __r
   }
 }
 
+// The same for rows of whole 16-byte pieces that a block holds in registers: a thread takes two groups of four neighbouring columns
+// of every input (16-byte loads of float32 partial sums, 8-byte loads of bfloat16 rows), and the inputs' sums of squares are reduced
+// over the block together, behind one pair of barriers.  Shared memory: MEAN_OF_NORMED_MAX * 33 floats (static).
+template <typename T>
+__global__ void mean_of_normed_vec_kernel(NormedInputs inputs, int count, float* __restrict__ out, int width, long long tokens, float eps) {
+  __shared__ float scratch[MEAN_OF_NORMED_MAX][33];
+  grid_dependency_wait();
+  allow_dependents();
+  const long long t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  auto value4 = [&](const NormedInput& in, int c) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (in.is_float) {
+      const float* p = (const float*)in.data + t * width + c;
+      for (int part = 0; part < in.parts; ++part) {
+        const float4 x = *reinterpret_cast<const float4*>(p + (long long)part * tokens * width);
+        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+      }
+    } else {
+      T x[4];
+      *reinterpret_cast<uint2*>(x) = *reinterpret_cast<const uint2*>((const T*)in.data + t * width + c);   // only taken for 16-bit T
+      v = make_float4(to_float<T>(x[0]), to_float<T>(x[1]), to_float<T>(x[2]), to_float<T>(x[3]));
+    }
+    return v;
+  };
+  float4 held[MEAN_OF_NORMED_MAX][2];
+  float sumsq[MEAN_OF_NORMED_MAX];
+#pragma unroll
+  for (int i = 0; i < MEAN_OF_NORMED_MAX; ++i) {
+    sumsq[i] = 0.f;
+    if (i < count) {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const int c = 4 * (threadIdx.x + k * blockDim.x);
+        held[i][k] = c < width ? value4(inputs.of[i], c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        sumsq[i] = fmaf(held[i][k].x, held[i][k].x, sumsq[i]);
+        sumsq[i] = fmaf(held[i][k].y, held[i][k].y, sumsq[i]);
+        sumsq[i] = fmaf(held[i][k].z, held[i][k].z, sumsq[i]);
+        sumsq[i] = fmaf(held[i][k].w, held[i][k].w, sumsq[i]);
+      }
+      sumsq[i] = warp_sum(sumsq[i]);
+      if (lane == 0) scratch[i][warp] = sumsq[i];
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+#pragma unroll
+    for (int i = 0; i < MEAN_OF_NORMED_MAX; ++i)
+      if (i < count) {
+        const float w = warp_sum(lane < warps ? scratch[i][lane] : 0.f);
+        if (lane == 0) scratch[i][32] = w;
+      }
+  }
+  __syncthreads();
+  const float share = 1.f / (float)count;
+  float inv[MEAN_OF_NORMED_MAX];
+#pragma unroll
+  for (int i = 0; i < MEAN_OF_NORMED_MAX; ++i) inv[i] = i < count ? rsqrtf(scratch[i][32] / (float)width + eps) : 0.f;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int c = 4 * (threadIdx.x + k * blockDim.x);
+    if (c >= width) break;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < MEAN_OF_NORMED_MAX; ++i)
+      if (i < count) {
+        const float4 w = *reinterpret_cast<const float4*>(inputs.of[i].weight + c);
+        acc.x += held[i][k].x * inv[i] * w.x; acc.y += held[i][k].y * inv[i] * w.y;
+        acc.z += held[i][k].z * inv[i] * w.z; acc.w += held[i][k].w * inv[i] * w.w;
+      }
+    *reinterpret_cast<float4*>(out + t * width + c) = make_float4(acc.x * share, acc.y * share, acc.z * share, acc.w * share);
+  }
+}
+
 }  // namespace pylon
 
 using namespace pylon;
@@ -196,6 +270,12 @@ extern "C" int pylon_mean_of_normed(const void* const* data, const float* const*
   int threads = 128;
   while (threads < 1024 && threads * MEAN_HELD < width) threads *= 2;
   const bool held = threads * MEAN_HELD >= width;
+  bool pieces = held && dtype == PYLON_DTYPE_BF16 && width % 4 == 0 && (uintptr_t)out % 16 == 0;   // rows of whole 16-byte pieces, blocks of a 16-bit dtype
+  for (int i = 0; i < count && pieces; ++i) pieces = (uintptr_t)data[i] % 16 == 0 && (uintptr_t)weights[i] % 16 == 0;
+  if (pieces) {
+    launch_dependent(mean_of_normed_vec_kernel<__nv_bfloat16>, dim3((unsigned)tokens), dim3(threads), 0, stream, inputs, count, out, width, (long long)tokens, eps);
+    PYLON_CHECK_LAUNCH("mean_of_normed");
+  }
 #define PYLON_MEAN(T, HELD) launch_dependent(mean_of_normed_kernel<T, HELD>, dim3((unsigned)tokens), dim3(threads), 0, stream, inputs, count, out, width, (long long)tokens, eps)
   if (dtype == PYLON_DTYPE_F32) { if (held) PYLON_MEAN(float, true); else PYLON_MEAN(float, false); }
   else if (dtype == PYLON_DTYPE_BF16) { if (held) PYLON_MEAN(__nv_bfloat16, true); else PYLON_MEAN(__nv_bfloat16, false); }
