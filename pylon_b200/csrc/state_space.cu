@@ -229,8 +229,10 @@ __global__ void ssm_recurrence_kernel(const float* __restrict__ xbc, const float
   }
 }
 
-// y: float32 [T, inner]; z: columns of proj from col_gate; out [T, inner] in T.  A block per (token, norm group).
-template <typename T>
+// y: float32 [T, inner]; z: columns of proj from col_gate; out [T, inner] in T.  A block per (token, norm group).  HELD: a thread
+// keeps its (at most SSM_NORM_HELD) gated values between the sum of squares and the result: y and z are read and silu taken once.
+constexpr int SSM_NORM_HELD = 8;
+template <typename T, bool HELD>
 __global__ void ssm_gated_norm_kernel(const float* __restrict__ y, const T* __restrict__ proj, long long ld, int col_gate,
                                       const float* __restrict__ weight, T* __restrict__ out, int inner, int norm_groups, float eps) {
   __shared__ float scratch[33];
@@ -240,16 +242,33 @@ __global__ void ssm_gated_norm_kernel(const float* __restrict__ y, const T* __re
   const int size = inner / norm_groups, first = part * size;
   const float* mine = y + (long long)t * inner + first;
   const T* gate = proj + (long long)t * ld + col_gate + first;
-  float sumsq = 0.f;
-  for (int e = threadIdx.x; e < size; e += blockDim.x) {
-    const float g = mine[e] * ssm_silu(to_float<T>(gate[e]));
-    sumsq = fmaf(g, g, sumsq);
-  }
-  sumsq = block_sum(sumsq, scratch);
-  const float inv = rsqrtf(sumsq / (float)size + eps);
   T* dst = out + (long long)t * inner + first;
-  for (int e = threadIdx.x; e < size; e += blockDim.x)
-    dst[e] = from_float<T>(mine[e] * ssm_silu(to_float<T>(gate[e])) * inv * weight[first + e]);
+  float sumsq = 0.f;
+  if (HELD) {
+    float held[SSM_NORM_HELD];
+#pragma unroll
+    for (int k = 0; k < SSM_NORM_HELD; ++k) {
+      const int e = threadIdx.x + k * blockDim.x;
+      held[k] = e < size ? mine[e] * ssm_silu(to_float<T>(gate[e])) : 0.f;
+      sumsq = fmaf(held[k], held[k], sumsq);
+    }
+    sumsq = block_sum(sumsq, scratch);
+    const float inv = rsqrtf(sumsq / (float)size + eps);
+#pragma unroll
+    for (int k = 0; k < SSM_NORM_HELD; ++k) {
+      const int e = threadIdx.x + k * blockDim.x;
+      if (e < size) dst[e] = from_float<T>(held[k] * inv * weight[first + e]);
+    }
+  } else {
+    for (int e = threadIdx.x; e < size; e += blockDim.x) {
+      const float g = mine[e] * ssm_silu(to_float<T>(gate[e]));
+      sumsq = fmaf(g, g, sumsq);
+    }
+    sumsq = block_sum(sumsq, scratch);
+    const float inv = rsqrtf(sumsq / (float)size + eps);
+    for (int e = threadIdx.x; e < size; e += blockDim.x)
+      dst[e] = from_float<T>(mine[e] * ssm_silu(to_float<T>(gate[e])) * inv * weight[first + e]);
+  }
 }
 
 }  // namespace pylon
@@ -309,8 +328,18 @@ static int launch_state_space(const void* proj_v, long long ld, const float* con
     else PYLON_SSM_RECURRENCE(32, 32);
 #undef PYLON_SSM_RECURRENCE
   }
-  launch_dependent(ssm_gated_norm_kernel<T>, dim3((unsigned)num_tokens * norm_groups), dim3(128), 0, stream, y, proj, ld, 0, norm_weight,
-                   out, inner, norm_groups, norm_eps);
+  {
+    // as many threads as leave each at most SSM_NORM_HELD values of a norm group (by the sizes alone)
+    const int size = inner / norm_groups;
+    int threads = 128;
+    while (threads < 1024 && threads * SSM_NORM_HELD < size) threads *= 2;
+    if (threads * SSM_NORM_HELD >= size)
+      launch_dependent(ssm_gated_norm_kernel<T, true>, dim3((unsigned)num_tokens * norm_groups), dim3(threads), 0, stream, y, proj, ld, 0, norm_weight,
+                       out, inner, norm_groups, norm_eps);
+    else
+      launch_dependent(ssm_gated_norm_kernel<T, false>, dim3((unsigned)num_tokens * norm_groups), dim3(threads), 0, stream, y, proj, ld, 0, norm_weight,
+                       out, inner, norm_groups, norm_eps);
+  }
   PYLON_CHECK_LAUNCH("state_space");
 }
 
