@@ -13,7 +13,10 @@
 //   experts_plan      one block: tokens per expert, the experts' first tiles, a slot for every pair
 //   experts_product   a block per (row tile, column tile): rows gathered by slot, the expert's matrix, float32 sums in a
 //                     fixed order of k; with GLU the gate and up tiles side by side and act(gate) * up written
-//   experts_product_mma   the same on tensor cores (bfloat16, mma.sync m16n8k16)
+//   experts_product_mma   the same on tensor cores (bfloat16, mma.sync m16n8k16), the matrices through a ring of cp.async stages:
+//                     the products of a step of few tokens
+//   experts_sort_rows the tokens' rows copied into the order of their slots, for a step of many tokens: its products are the
+//                     grouped form of the tcgen05 kernel (gemm_tcgen05.cu) over row tiles of 128 slots
 //   experts_gather    out[t] = sum_k share[t, k] * y[slot(t, k)], float32
 // A row's sums do not depend on where in a tile it lies or what else is in the batch.
 #include "common.cuh"
