@@ -1287,9 +1287,13 @@ extern "C" int pylon_attention_decode_blocks() {
 
 // Scratch floats a call needs: `num_splits` splits of the tiled kernel over `total_tokens`
 // tokens (none for one split) and the decode kernel's segment slots (none for decode_blocks = 0).
+// The splits' part of the scratch: partial outputs and their log-sums, rounded up to whole 16-byte pieces, since the decode kernel's
+// segments lie behind it and are read as float4 (an odd number of query heads times an odd number of tokens would leave them askew).
+static inline long long split_scratch_floats(int num_splits, long long items) { return ((long long)num_splits * items * (D + 1) + 3) & ~3LL; }
+
 extern "C" long long pylon_attention_scratch_floats(int num_splits, int total_tokens, int nq, int num_rows, int nkv, int decode_blocks) {
   long long floats = 0;
-  if (num_splits > 1) floats += (long long)num_splits * total_tokens * nq * (D + 1);
+  if (num_splits > 1) floats += split_scratch_floats(num_splits, (long long)total_tokens * nq);
   if (decode_blocks > 0) floats += ((long long)num_rows * nkv + decode_blocks) * SMALL_ROWS * (D + 1);
   return floats;
 }
@@ -1372,7 +1376,7 @@ extern "C" int pylon_paged_attention_mma_masked(const void* q, long long q_strid
   if (num_splits > 1) {
     p.partial_out = scratch;
     p.partial_lse = scratch + (size_t)num_splits * items * D;
-    decode_scratch = scratch + (size_t)num_splits * items * (D + 1);
+    decode_scratch = scratch + split_scratch_floats(num_splits, items);
   }
   const size_t slots = (size_t)num_rows * nkv + (maybe_small ? decode_blocks : 0);
   p.decode_out = decode_scratch;
