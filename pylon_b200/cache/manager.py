@@ -104,7 +104,7 @@ class CacheGroup:
         # A step's tokens plus what its first token reads before itself (a window, or the part of
         # its chunk that lies before it), not page aligned.
         span = min(capacity, self.need.reach - 1 + max(1, max_step_tokens))
-        return min(full, self.pages_for(span) + 1)
+        return min(full, self.pages_for(span) + 1 + self.pages_for(self.need.keep_first))   # and the pages of the first tokens, which stay
 
     def bytes_per_token(self, element_size: Optional[int] = None) -> int:
         if element_size is None:
@@ -292,9 +292,10 @@ class CacheManager:
                 continue
             first_needed = group.need.first_needed(request.length)   # oldest key a later token reads
             dead_pages = max(0, first_needed) // self.page_size  # logical pages wholly before it
+            kept_pages = group.pages_for(group.need.keep_first)  # ... but the pages of the first tokens stay readable
             table = request.tables[g]
-            freed = [table[i] for i in range(min(dead_pages, len(table))) if table[i] >= 0]
-            for i in range(min(dead_pages, len(table))):
+            freed = [table[i] for i in range(kept_pages, min(dead_pages, len(table))) if table[i] >= 0]
+            for i in range(kept_pages, min(dead_pages, len(table))):
                 table[i] = -1
             group.pool.release(freed)
 

@@ -710,3 +710,245 @@ class ZemavikConfig:
                     gate_rank=layer.delta.gate_rank if gate is None else int(gate[0])))
             layers.append(layer)
         return replace(self, layers=tuple(layers))
+
+
+# ---------------------------------------------------------------------------------------
+@dataclass(frozen=True)
+class RirusunAttention:
+    """The attending half of a Rirusun ``parallel`` mixer: grouped-query attention without rotation, q and k RMS-normed over their
+    whole rows, scores times ``scale`` plus a learnt bias by distance (a table of logarithmic buckets that ends at ``bias_max``),
+    a sliding window of ``window`` positions (``None``: every earlier key) that always keeps the first ``keep_first`` positions,
+    and a learnt sink per head in the softmax's denominator."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    bias_max: int
+    window: Optional[int] = None
+    keep_first: int = 0
+    bias_rows: Optional[int] = None    # rows of the bias table: the checkpoint's tensor shape gives them (a configuration written for random weights names them)
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "RirusunAttention":
+        heads, kv_heads = _positive_int(data, "heads"), _positive_int(data, "kv_heads")
+        if heads % kv_heads:
+            raise ConfigError(f"{where}: {heads} heads cannot be grouped over {kv_heads} kv_heads")
+        mask = data.get("mask")
+        window, keep = None, 0
+        if mask is not None:
+            mask = _mapping(data, "mask")
+            window = _positive_int(mask, "size")
+            keep = int(mask.get("keep_first") or 0)
+            if keep < 0:
+                raise ConfigError(f"{where}: mask.keep_first must not be negative")
+        return cls(heads, kv_heads, _positive_int(data, "dim"), _positive_int(data, "vdim"), _number(data, "scale"), _positive_int(data, "bias_max"),
+                   window, keep, None if data.get("bias_rows") is None else _positive_int(data, "bias_rows"))
+
+    def to_dict(self) -> dict[str, Any]:
+        data: dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
+                                "bias_max": self.bias_max}
+        if self.window is not None:
+            data["mask"] = {"size": self.window, "keep_first": self.keep_first}
+        if self.bias_rows is not None:
+            data["bias_rows"] = self.bias_rows
+        return data
+
+
+@dataclass(frozen=True)
+class RirusunRecurrent:
+    """The recurrent half of a Rirusun ``parallel`` mixer: two branches of ``width`` channels, one through a causal convolution of
+    ``conv`` taps and a gated linear recurrence whose gates are maps of ``blocks`` equal parts of the channels."""
+
+    width: int
+    blocks: int
+    conv: int
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "RirusunRecurrent":
+        made = cls(_positive_int(data, "width"), _positive_int(data, "blocks"), _positive_int(data, "conv"))
+        if made.width % made.blocks:
+            raise ConfigError(f"{where}: {made.width} channels cannot be cut into {made.blocks} equal parts")
+        return made
+
+    def to_dict(self) -> dict[str, Any]:
+        return {"width": self.width, "blocks": self.blocks, "conv": self.conv}
+
+
+@dataclass(frozen=True)
+class RirusunFeedForward:
+    """A mixture of ``experts`` ungated feed-forwards of inner width ``ff`` of which a token uses ``top``, chosen by sigmoid scores
+    with a correction among the experts of the ``groups_keep`` best of ``groups`` groups, plus (``shared_ff``) one expert that every
+    token goes through behind a sigmoid gate."""
+
+    ff: int
+    experts: int
+    top: int
+    groups: Optional[int] = None
+    groups_keep: Optional[int] = None
+    shared_ff: Optional[int] = None
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], where: str) -> "RirusunFeedForward":
+        kind = _require(data, "kind", str)
+        if kind != "moe":
+            raise ConfigError(f"{where}: unknown feed-forward kind {kind!r} (moe)")
+        router = _mapping(data, "router")
+        experts, top = _positive_int(router, "experts"), _positive_int(router, "top")
+        groups = keep = None
+        if router.get("groups") is not None:
+            groups, keep = _positive_int(_mapping(router, "groups"), "count"), _positive_int(_mapping(router, "groups"), "keep")
+            if experts % groups or keep > groups:
+                raise ConfigError(f"{where}: {experts} experts in {groups} groups of which {keep} are kept")
+        if top > (experts if groups is None else keep * (experts // groups)):
+            raise ConfigError(f"{where}: a token cannot use {top} of the experts it may choose from")
+        shared = data.get("shared")
+        return cls(_positive_int(_mapping(data, "expert"), "ff"), experts, top, groups, keep,
+                   None if shared is None else _positive_int(_mapping(data, "shared"), "ff"))
+
+    def to_dict(self) -> dict[str, Any]:
+        router: dict[str, Any] = {"experts": self.experts, "top": self.top}
+        if self.groups is not None:
+            router["groups"] = {"count": self.groups, "keep": self.groups_keep}
+        data: dict[str, Any] = {"kind": "moe", "expert": {"ff": self.ff}, "router": router}
+        if self.shared_ff is not None:
+            data["shared"] = {"ff": self.shared_ff}
+        return data
+
+
+@dataclass(frozen=True)
+class RirusunLayer:
+    """One layer: its mixer - ``parallel`` (``left`` attends, ``right`` is the gated linear recurrence, their outputs added with a
+    factor each), ``mlstm`` (a matrix memory per head; ``memory`` = (heads, dim, vdim, gate_cap)) or ``latent_attention`` (``latent``
+    holds its sizes as a :class:`FikeraxLayer` does) - and its feed-forward, or none."""
+
+    kind: str
+    left: Optional[RirusunAttention] = None
+    right: Optional[RirusunRecurrent] = None
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    memory: Optional[tuple] = None
+    latent: Optional[tuple] = None      # (heads, dim, rot_dim, vdim, kv_rank, scale, RotarySpec or None)
+    mlp: Optional[RirusunFeedForward] = None
+
+    KINDS: ClassVar[tuple[str, ...]] = ("parallel", "mlstm", "latent_attention")
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any], index: int) -> "RirusunLayer":
+        kind, where = _require(data, "type", str), f"layer {index}"
+        if kind not in cls.KINDS:
+            raise ConfigError(f"{where}: unknown type {kind!r} ({', '.join(cls.KINDS)})")
+        mixer = _mapping(data, "mixer")
+        mlp = data.get("mlp")
+        if mlp is not None and not isinstance(mlp, dict):
+            raise ConfigError(f"{where}: 'mlp' must be an object or null")
+        feed_forward = None if mlp is None else RirusunFeedForward.from_dict(mlp, where)
+        if kind == "parallel":
+            return cls(kind, left=RirusunAttention.from_dict(_mapping(mixer, "left"), where), right=RirusunRecurrent.from_dict(_mapping(mixer, "right"), where),
+                       left_scale=_number(mixer, "left_scale"), right_scale=_number(mixer, "right_scale"), mlp=feed_forward)
+        if kind == "mlstm":
+            cap = _number(mixer, "gate_cap")
+            if not cap > 0:
+                raise ConfigError(f"{where}: gate_cap must be positive")
+            return cls(kind, memory=(_positive_int(mixer, "heads"), _positive_int(mixer, "dim"), _positive_int(mixer, "vdim"), cap), mlp=feed_forward)
+        rot = None
+        rot_dim = _positive_int(mixer, "rot_dim")
+        if mixer.get("rot") is not None:
+            rot = RotarySpec.from_dict(_mapping(mixer, "rot"), where, ("factor", "original", "fast", "slow"))
+            if rot.dims > rot_dim:
+                raise ConfigError(f"{where}: rot.dims {rot.dims} exceeds rot_dim {rot_dim}")
+        return cls(kind, latent=(_positive_int(mixer, "heads"), _positive_int(mixer, "dim"), rot_dim, _positive_int(mixer, "vdim"),
+                                 _positive_int(mixer, "kv_rank"), _number(mixer, "scale"), rot), mlp=feed_forward)
+
+    def to_dict(self) -> dict[str, Any]:
+        if self.kind == "parallel":
+            mixer: dict[str, Any] = {"left": self.left.to_dict(), "left_scale": self.left_scale, "right": self.right.to_dict(), "right_scale": self.right_scale}
+        elif self.kind == "mlstm":
+            mixer = dict(zip(("heads", "dim", "vdim", "gate_cap"), self.memory))
+        else:
+            mixer = dict(zip(("heads", "dim", "rot_dim", "vdim", "kv_rank", "scale"), self.latent[:6]))
+            if self.latent[6] is not None:
+                mixer["rot"] = self.latent[6].to_dict()
+        return {"type": self.kind, "mixer": mixer, "mlp": None if self.mlp is None else self.mlp.to_dict()}
+
+
+@dataclass(frozen=True)
+class RirusunConfig:
+    """Rirusun: a decoder whose layers each read one norm - a scaled tanh with weight and bias instead of statistics - and add
+    mixer and feed-forward to the stream side by side.  The mixers are, in an order the configuration lists, windowed attention
+    with kept first tokens, distance bias and sink beside a gated linear recurrence; a matrix memory with exponential gates; and
+    latent attention with YaRN-scaled rotation.  The feed-forward is a mixture of experts with grouped sigmoid routing and a
+    gated shared expert.  The embedding is scaled, the head is a tensor of its own, and a span of layers ``loop`` = (start, stop,
+    times) runs several times in a row, each pass with caches of its own and nothing between the passes.
+
+    ``config.json`` names the model by ``"architecture": "Rirusun"``.  Field names follow its keys.
+    """
+
+    architecture: ClassVar[str] = "Rirusun"
+
+    vocab: int
+    width: int
+    layers: tuple[RirusunLayer, ...]
+    norm_eps: float
+    embedding_scale: float = 1.0
+    loop: Optional[tuple[int, int, int]] = None
+    eos_token_ids: tuple[int, ...] = field(default_factory=tuple)
+
+    def __post_init__(self) -> None:
+        if not self.layers:
+            raise ConfigError("a model needs at least one layer")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        if self.loop is not None:
+            start, stop, times = self.loop
+            if not 0 <= start <= stop <= len(self.layers) or times < 1:
+                raise ConfigError(f"loop {start} .. {stop} x {times} does not fit {len(self.layers)} layers")
+
+    @classmethod
+    def from_dict(cls, data: Mapping[str, Any]) -> "RirusunConfig":
+        layers = _require(data, "layers", list)
+        eos = data.get("eos_token_id")
+        loop = data.get("loop")
+        if loop is not None and not isinstance(loop, dict):
+            raise ConfigError("'loop' must be an object or null")
+        return cls(
+            vocab=_positive_int(data, "vocab"),
+            width=_positive_int(data, "width"),
+            layers=tuple(RirusunLayer.from_dict(layer, index) for index, layer in enumerate(layers)),
+            norm_eps=_number(_mapping(data, "norm"), "eps"),
+            embedding_scale=1.0 if data.get("embedding") is None else _number(_mapping(data, "embedding"), "scale"),
+            loop=None if loop is None else (int(_require(loop, "start", int)), int(_require(loop, "stop", int)), _positive_int(loop, "times")),
+            eos_token_ids=() if eos is None else ((eos,) if isinstance(eos, int) else tuple(int(x) for x in eos)),
+        )
+
+    def to_dict(self) -> dict[str, Any]:
+        data: dict[str, Any] = {
+            "architecture": self.architecture, "vocab": self.vocab, "width": self.width, "embedding": {"scale": self.embedding_scale},
+            "layers": [layer.to_dict() for layer in self.layers], "norm": {"eps": self.norm_eps},
+        }
+        if self.loop is not None:
+            data["loop"] = {"start": self.loop[0], "stop": self.loop[1], "times": self.loop[2]}
+        if self.eos_token_ids:
+            data["eos_token_id"] = list(self.eos_token_ids)
+        return data
+
+    def run_order(self) -> list[int]:
+        """The layer of every run: the layers before the loop, the loop's span ``times`` times, the rest."""
+        if self.loop is None:
+            return list(range(len(self.layers)))
+        start, stop, times = self.loop
+        return list(range(start)) + list(range(start, stop)) * times + list(range(stop, len(self.layers)))
+
+    def with_checkpoint_sizes(self, shape_of) -> "RirusunConfig":
+        """The sizes that only tensor shapes give: ``shape_of(name)`` is a checkpoint tensor's shape, or ``None``."""
+        from dataclasses import replace
+
+        layers = []
+        for index, layer in enumerate(self.layers):
+            if layer.kind == "parallel":
+                table = shape_of(f"l{index}.mix.left.rel")
+                if table is not None:
+                    layer = replace(layer, left=replace(layer.left, bias_rows=int(table[0])))
+            layers.append(layer)
+        return replace(self, layers=tuple(layers))

@@ -11,7 +11,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Callable, Mapping, Optional
 
-from pylon_b200.config.model_config import ConfigError, FikeraxConfig, Qwen3Config, VopepelConfig, ZemavikConfig
+from pylon_b200.config.model_config import ConfigError, FikeraxConfig, Qwen3Config, RirusunConfig, VopepelConfig, ZemavikConfig
 from pylon_b200.parts.spec import ModelSpec
 
 
@@ -68,6 +68,9 @@ def _register_builtin() -> None:
     from pylon_b200.models.zemavik import zemavik_spec
 
     register_architecture(ZemavikConfig.architecture, ZemavikConfig, zemavik_spec)
+    from pylon_b200.models.rirusun import rirusun_spec
+
+    register_architecture(RirusunConfig.architecture, RirusunConfig, rirusun_spec)
 
 
 _register_builtin()

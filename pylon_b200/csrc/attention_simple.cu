@@ -14,6 +14,9 @@
 // whose score is the sink as it stands, neither scaled nor capped.  Key and value rows may lie
 // `k_row_stride` / `v_row_stride` elements apart (0: their own widths), so that the values can be the first
 // `dv` columns of the key rows themselves (one latent row per token, read by every head: nkv = 1).
+// With `keep_first` n > 0 a window never hides the keys at positions j < n: a token sees j <= p with p - j < window or j < n.
+// With `bias` (float32 [bias_rows, nq]) the scaled (and capped) score of the key d = p - j positions back gets
+// bias[min(d, bias_rows - 1), h] added: a learnt function of the distance that is constant from bias_rows - 1 on.
 //
 // The keys of a token are walked in chunks of 128 positions aligned at position 0, so a
 // token's result depends on its position only, not on how the step was cut or batched.
@@ -30,7 +33,8 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
     const T* __restrict__ v_pages, T* __restrict__ out, const int* __restrict__ positions,
     const int* __restrict__ token_row, const int* __restrict__ block_table, int table_width, int page_size,
     int num_pages, int nq, int nkv, int d, int dv, int window, int chunk, float softcap, float scale,
-    const float* __restrict__ sinks, long long k_row_stride, long long v_row_stride) {
+    const float* __restrict__ sinks, long long k_row_stride, long long v_row_stride, int keep_first, const float* __restrict__ bias,
+    int bias_rows) {
   extern __shared__ long long shared[];
   long long* offsets = shared;                                      // [128] cache rows of the keys (page, head, slot), -1: none
   float* probs = reinterpret_cast<float*>(offsets + SIMPLE_THREADS);  // [128]
@@ -55,11 +59,13 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
   float running_max = sinks ? sinks[h] : -INFINITY, running_sum = sinks ? 1.f : 0.f;
   __syncthreads();
 
-  for (int c0 = (lo / SIMPLE_THREADS) * SIMPLE_THREADS; c0 <= pos; c0 += SIMPLE_THREADS) {
+  const int kept = keep_first < lo ? keep_first : lo;   // the keys before the window that stay visible: [0, kept)
+  for (int c0 = kept > 0 ? 0 : (lo / SIMPLE_THREADS) * SIMPLE_THREADS; c0 <= pos; c0 += SIMPLE_THREADS) {
+    if (c0 >= kept && c0 + SIMPLE_THREADS <= lo) continue;   // a chunk between the kept keys and the window (the same for all threads)
     const int j = c0 + tid;
     float score = -INFINITY;
     long long offset = -1;
-    if (j >= lo && j <= pos) {
+    if ((j >= lo || j < kept) && j <= pos) {
       const int page = table[j / page_size];
       if (page >= 0 && page < num_pages) {
         offset = ((long long)page * nkv + kv_head) * page_size + j % page_size;
@@ -67,6 +73,7 @@ __global__ void __launch_bounds__(SIMPLE_THREADS) paged_attention_simple_kernel(
         float dot = 0.f;
         for (int e = 0; e < d; ++e) dot = fmaf(qs[e], to_float<T>(krow[e]), dot);
         score = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
+        if (bias) score += bias[(size_t)(pos - j < bias_rows ? pos - j : bias_rows - 1) * nq + h];
       }
     }
     offsets[tid] = offset;
@@ -113,7 +120,7 @@ extern "C" int pylon_paged_attention_simple(const void* q, long long q_token_str
                                             int page_size, int num_pages, int nq, int nkv, int d, int dv, int window,
                                             int chunk, float softcap, float scale, const float* sinks,
                                             long long k_row_stride, long long v_row_stride, int num_tokens, int dtype,
-                                            cudaStream_t stream) {
+                                            int keep_first, const float* bias, int bias_rows, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (d < 1 || d > 2048) PYLON_REFUSE("paged_attention_simple: head size %d is outside 1..2048", d);
   if (k_row_stride == 0) k_row_stride = d;
@@ -122,6 +129,8 @@ extern "C" int pylon_paged_attention_simple(const void* q, long long q_token_str
   if (dv < 1 || dv > SIMPLE_THREADS * SIMPLE_MAX_DIMS_PER_THREAD)
     PYLON_REFUSE("paged_attention_simple: value size %d is outside 1..%d", dv, SIMPLE_THREADS * SIMPLE_MAX_DIMS_PER_THREAD);
   if (chunk < 0 || softcap < 0.f) PYLON_REFUSE("paged_attention_simple: chunk %d, soft cap %f", chunk, softcap);
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) PYLON_REFUSE("paged_attention_simple: %d kept first keys (not with chunks)", keep_first);
+  if (bias && bias_rows < 1) PYLON_REFUSE("paged_attention_simple: a bias table of %d rows", bias_rows);
   if (nkv < 1 || nq < 1 || nq % nkv) PYLON_REFUSE("paged_attention_simple: %d query heads over %d KV heads", nq, nkv);
   if (nq > 65535) PYLON_REFUSE("paged_attention_simple: %d query heads", nq);
   if (page_size < 1 || table_width < 1 || window < 0)
@@ -131,12 +140,13 @@ extern "C" int pylon_paged_attention_simple(const void* q, long long q_token_str
   if (dtype == PYLON_DTYPE_F32)
     paged_attention_simple_kernel<float><<<grid, SIMPLE_THREADS, smem, stream>>>(
         (const float*)q, q_token_stride, (const float*)k_pages, (const float*)v_pages, (float*)out, positions,
-        token_row, block_table, table_width, page_size, num_pages, nq, nkv, d, dv, window, chunk, softcap, scale, sinks, k_row_stride, v_row_stride);
+        token_row, block_table, table_width, page_size, num_pages, nq, nkv, d, dv, window, chunk, softcap, scale, sinks, k_row_stride, v_row_stride,
+        keep_first, bias, bias_rows);
   else if (dtype == PYLON_DTYPE_BF16)
     paged_attention_simple_kernel<__nv_bfloat16><<<grid, SIMPLE_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)q, q_token_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
         (__nv_bfloat16*)out, positions, token_row, block_table, table_width, page_size, num_pages, nq, nkv, d, dv,
-        window, chunk, softcap, scale, sinks, k_row_stride, v_row_stride);
+        window, chunk, softcap, scale, sinks, k_row_stride, v_row_stride, keep_first, bias, bias_rows);
   else
     PYLON_REFUSE("paged_attention_simple: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("paged_attention_simple");

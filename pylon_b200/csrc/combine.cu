@@ -24,7 +24,17 @@ __global__ void side_by_side_kernel(const float* __restrict__ a, const float* __
 __device__ __forceinline__ float unit_activation(float x, int kind) {
   if (kind == 0) return x / (1.f + expf(-x));                                       // silu
   if (kind == 1) return fmaxf(x, 0.f);                                              // relu
+  if (kind == 3) return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));           // gelu, exact (erf) form
   return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));   // gelu, tanh form
+}
+
+// In place: x <- act(x), element by element.
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ x, long long total, int kind) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item < total) x[item] = from_float<T>(unit_activation(to_float<T>(x[item]), kind));
 }
 
 template <typename T>
@@ -220,6 +230,28 @@ __global__ void mean_of_normed_vec_kernel(NormedInputs inputs, int count, float*
   }
 }
 
+// out[t, c] = sum_i scale_i * y_i[t, c] over up to four inputs, each a block in the compute dtype or float32 partial sums.
+template <typename T>
+__global__ void weighted_sum_kernel(NormedInputs inputs, float4 scales, int count, float* __restrict__ out, long long per_part) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= per_part) return;
+  const float scale[4] = {scales.x, scales.y, scales.z, scales.w};
+  float acc = 0.f;
+  for (int i = 0; i < count; ++i) {
+    const NormedInput& in = inputs.of[i];
+    float v = 0.f;
+    if (in.is_float) {
+      for (int part = 0; part < in.parts; ++part) v += ((const float*)in.data)[(long long)part * per_part + item];
+    } else {
+      v = to_float<T>(((const T*)in.data)[item]);
+    }
+    acc = fmaf(scale[i], v, acc);
+  }
+  out[item] = acc;
+}
+
 }  // namespace pylon
 
 using namespace pylon;
@@ -238,7 +270,7 @@ extern "C" int pylon_side_by_side(const float* a, const float* b, void* out, int
 extern "C" int pylon_gated_unit(const void* gate_up, long long ld, const float* bias, void* out, int tokens, int inner, int kind, int dtype,
                                 cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (inner <= 0 || kind < 0 || kind > 2) PYLON_REFUSE("gated_unit: inner width %d, activation %d", inner, kind);
+  if (inner <= 0 || kind < 0 || kind > 3) PYLON_REFUSE("gated_unit: inner width %d, activation %d", inner, kind);
   const long long total = (long long)tokens * inner;
   const dim3 grid((unsigned)((total + 255) / 256));
   if (dtype == PYLON_DTYPE_F32) launch_dependent(gated_unit_kernel<float>, grid, dim3(256), 0, stream, (const float*)gate_up, ld, bias, (float*)out, inner, total, kind);
@@ -282,4 +314,37 @@ extern "C" int pylon_mean_of_normed(const void* const* data, const float* const*
   else PYLON_REFUSE("mean_of_normed: unknown dtype %d", dtype);
 #undef PYLON_MEAN
   PYLON_CHECK_LAUNCH("mean_of_normed");
+}
+
+// outputs[i]: [parts_i, T, width] float32 partial sums (is_float_i) or [T, width] in dtype; out float32 [T, width] = sum_i scales[i] * outputs[i].
+extern "C" int pylon_weighted_sum(const void* const* outputs, const int* parts, const int* is_float, const float* scales, int count, float* out,
+                                  long long total, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (count < 1 || count > MEAN_OF_NORMED_MAX) PYLON_REFUSE("weighted_sum: %d inputs (1 to %d)", count, MEAN_OF_NORMED_MAX);
+  NormedInputs inputs;
+  float factor[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int i = 0; i < count; ++i) {
+    inputs.of[i].data = outputs[i];
+    inputs.of[i].weight = nullptr;
+    inputs.of[i].parts = parts[i];
+    inputs.of[i].is_float = is_float[i];
+    factor[i] = scales[i];
+  }
+  const float4 packed = make_float4(factor[0], factor[1], factor[2], factor[3]);
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == PYLON_DTYPE_F32) launch_dependent(weighted_sum_kernel<float>, grid, dim3(256), 0, stream, inputs, packed, count, out, total);
+  else if (dtype == PYLON_DTYPE_BF16) launch_dependent(weighted_sum_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, inputs, packed, count, out, total);
+  else PYLON_REFUSE("weighted_sum: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("weighted_sum");
+}
+
+// x: [total] in dtype, in place.
+extern "C" int pylon_activation(void* x, long long total, int kind, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (kind < 0 || kind > 3) PYLON_REFUSE("activation: kind %d", kind);
+  const dim3 grid((unsigned)((total + 255) / 256));
+  if (dtype == PYLON_DTYPE_F32) launch_dependent(activation_kernel<float>, grid, dim3(256), 0, stream, (float*)x, total, kind);
+  else if (dtype == PYLON_DTYPE_BF16) launch_dependent(activation_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, total, kind);
+  else PYLON_REFUSE("activation: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("activation");
 }

@@ -706,6 +706,48 @@ __global__ void qk_norm_mix_kv_write_kernel(T* __restrict__ qkv, const float* __
   }
 }
 
+// The same cache write for attention whose q and k are RMS-normed over their whole rows, all heads of a token at once, with weights
+// as long as those rows (q_weight [nq * d], k_weight [nkv * d]).  One block per token: the two sums of squares, then q back in
+// place, k and v into their page slots.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_whole_norm_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                                                                     float eps, const int* __restrict__ positions, const int* __restrict__ token_row,
+                                                                     const int* __restrict__ block_table, int table_width, int page_size,
+                                                                     T* __restrict__ k_pages, T* __restrict__ v_pages, int num_pages, int nq, int nkv, int d,
+                                                                     int dv, int* __restrict__ error) {
+  __shared__ float scratch[34];
+  grid_dependency_wait();
+  allow_dependents();
+  const int t = blockIdx.x;
+  const int row = token_row[t];
+  if (row < 0) return;   // a padding token: it belongs to no request
+  const int q_size = nq * d, k_size = nkv * d, v_size = nkv * dv;
+  T* q = qkv + (long long)t * (q_size + k_size + v_size);
+  const T* k = q + q_size;
+  const T* v = k + k_size;
+  float q_squares = 0.f, k_squares = 0.f;
+  for (int e = threadIdx.x; e < q_size; e += blockDim.x) { const float x = to_float<T>(q[e]); q_squares = fmaf(x, x, q_squares); }
+  for (int e = threadIdx.x; e < k_size; e += blockDim.x) { const float x = to_float<T>(k[e]); k_squares = fmaf(x, x, k_squares); }
+  const float q_inv = rsqrtf(block_sum(q_squares, scratch) / (float)q_size + eps);
+  const float k_inv = rsqrtf(block_sum(k_squares, scratch) / (float)k_size + eps);
+  for (int e = threadIdx.x; e < q_size; e += blockDim.x) q[e] = from_float<T>(to_float<T>(q[e]) * q_inv * q_weight[e]);
+  const int pos = positions[t];
+  const int logical = pos / page_size;
+  const int page = logical < table_width ? block_table[(size_t)row * table_width + logical] : -1;
+  if (page < 0 || page >= num_pages) {   // never for a prepared step: nothing is written, and the host is told
+    if (threadIdx.x == 0 && error) atomicExch(error, PYLON_ERROR_BAD_PAGE);
+    return;
+  }
+  for (int e = threadIdx.x; e < k_size; e += blockDim.x) {
+    const int head = e / d, c = e % d;
+    k_pages[(((size_t)page * nkv + head) * page_size + pos % page_size) * d + c] = from_float<T>(to_float<T>(k[e]) * k_inv * k_weight[e]);
+  }
+  for (int e = threadIdx.x; e < v_size; e += blockDim.x) {
+    const int head = e / dv, c = e % dv;
+    v_pages[(((size_t)page * nkv + head) * page_size + pos % page_size) * dv + c] = v[e];
+  }
+}
+
 }  // namespace pylon
 
 using namespace pylon;
@@ -991,4 +1033,21 @@ extern "C" int pylon_qk_norm_mix_kv_write(void* qkv, const float* q_weight, cons
                                              block_table, table_width, page_size, k_pages, v_pages, num_pages, nq, nkv, d, dv, num_tokens,
                                              error, stream);
   PYLON_REFUSE("qk_norm_mix_kv_write: unknown dtype %d", dtype);
+}
+
+// qkv [T, nq d + nkv d + nkv dv] contiguous; q_weight float32 [nq d], k_weight float32 [nkv d]: see qk_whole_norm_kv_write_kernel.
+extern "C" int pylon_qk_whole_norm_kv_write(void* qkv, const float* q_weight, const float* k_weight, float eps, const int* positions, const int* token_row,
+                                            const int* block_table, int table_width, int page_size, void* k_pages, void* v_pages, int num_pages, int nq,
+                                            int nkv, int d, int dv, int num_tokens, int dtype, int* error, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (d < 1 || dv < 1 || nq < 1 || nkv < 1 || page_size < 1 || table_width < 1 || !q_weight || !k_weight)
+    PYLON_REFUSE("qk_whole_norm_kv_write: sizes %d/%d, heads %d/%d, page size %d, table width %d, or a weight is missing", d, dv, nq, nkv, page_size, table_width);
+  if (dtype == PYLON_DTYPE_F32)
+    launch_dependent(qk_whole_norm_kv_write_kernel<float>, dim3((unsigned)num_tokens), dim3(256), 0, stream, (float*)qkv, q_weight, k_weight, eps, positions,
+                     token_row, block_table, table_width, page_size, (float*)k_pages, (float*)v_pages, num_pages, nq, nkv, d, dv, error);
+  else if (dtype == PYLON_DTYPE_BF16)
+    launch_dependent(qk_whole_norm_kv_write_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(256), 0, stream, (__nv_bfloat16*)qkv, q_weight, k_weight, eps,
+                     positions, token_row, block_table, table_width, page_size, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, num_pages, nq, nkv, d, dv, error);
+  else PYLON_REFUSE("qk_whole_norm_kv_write: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("qk_whole_norm_kv_write");
 }

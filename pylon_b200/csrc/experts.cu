@@ -4,6 +4,12 @@
 //     chosen  = the `top` largest z (the lower index wins a tie),   share = softmax over the chosen z only
 //     out     = sum over chosen e of share_e * W_down,e (act(W_gate,e h) * (W_up,e h))
 //
+// A second way of routing (RouteScored): the scores are s = sigmoid(z); the choice goes by s + correction (a learnt vector), and only
+// among the experts of the `keep` best of `groups` equal groups of neighbours, a group's worth being the sum of its two largest choice
+// scores (of its one, if it has one expert); share = s of the chosen (without the correction), divided by their sum plus share_eps.  The
+// router matrix may have `extra` rows behind the experts': their logits leave as sigmoid(z) in extra_out [T, extra] (the gate of an
+// expert that every token goes through, say).  An ungated expert is W_down act(W_up h): the first product applies act itself.
+//
 // Nothing here needs the host to know how many tokens an expert got, so the step stays one sequence of launches (and
 // can be captured): the (token, choice) pairs are sorted by expert into row tiles of ROWS slots, every expert's span
 // padded to whole tiles, and the grouped products run over the most tiles there can be; a tile beyond the last one, and
@@ -29,6 +35,7 @@ constexpr int EXPERT_ROWS = 32;   // slots to a row tile
 __device__ __forceinline__ float expert_activation(float x, int kind) {
   if (kind == 0) return x / (1.f + expf(-x));
   if (kind == 1) return fmaxf(x, 0.f);
+  if (kind == 3) return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));   // gelu, exact form
   return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 
@@ -70,6 +77,85 @@ __device__ __forceinline__ void route_choose(float* logits, int* __restrict__ ch
   for (int k = 32 + lane; k < top; k += 32) share[t * top + k] *= inv;
 }
 
+// How the scores are made and the choice is restricted; correction null: none; groups 0: no groups.
+struct RouteScored {
+  int on;                    // 0: the softmax form above; the rest is unused then
+  const float* correction;   // [experts] or null
+  int groups, keep;
+  float share_eps;
+  int extra;                 // rows of the router behind the experts'
+  float* extra_out;          // [T, extra]
+};
+
+// One warp.  logits [experts + extra] holds z; choice [experts] and worth [groups] are scratch.
+__device__ __forceinline__ void route_choose_scored(float* logits, float* choice, float* worth, int* __restrict__ chosen, float* __restrict__ share,
+                                                    long long t, int experts, int top, int lane, const RouteScored& mode) {
+  for (int x = lane; x < mode.extra; x += 32) mode.extra_out[t * mode.extra + x] = 1.f / (1.f + expf(-logits[experts + x]));
+  for (int e = lane; e < experts; e += 32) {
+    const float s = 1.f / (1.f + expf(-logits[e]));
+    logits[e] = s;
+    choice[e] = s + (mode.correction != nullptr ? mode.correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (mode.groups > 0) {
+    const int size = experts / mode.groups;
+    for (int g = lane; g < mode.groups; g += 32) {
+      float first = -INFINITY, second = -INFINITY;
+      for (int i = 0; i < size; ++i) {
+        const float c = choice[g * size + i];
+        if (c > first) { second = first; first = c; }
+        else if (c > second) second = c;
+      }
+      worth[g] = size > 1 ? first + second : first;
+    }
+    __syncwarp();
+    for (int k = 0; k < mode.keep; ++k) {   // the best group not yet kept, the lower index on a tie; a kept group's worth becomes +inf
+      float best = -INFINITY;
+      int where = 0x7fffffff;
+      for (int g = lane; g < mode.groups; g += 32) {
+        const float w = worth[g];
+        if (w != INFINITY && (w > best || where == 0x7fffffff)) { best = w; where = g; }
+      }
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_where = __shfl_xor_sync(0xffffffffu, where, offset);
+        if (other_where != 0x7fffffff && (where == 0x7fffffff || other > best || (other == best && other_where < where))) { best = other; where = other_where; }
+      }
+      if (lane == 0 && where != 0x7fffffff) worth[where] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (worth[e / size] != INFINITY) choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int where = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float c = choice[e];
+      if (c > best) { best = c; where = e; }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+      const int other_where = __shfl_xor_sync(0xffffffffu, where, offset);
+      if (other > best || (other == best && other_where < where)) { best = other; where = other_where; }
+    }
+    if (where == 0x7fffffff) where = 0;
+    const float s = logits[where];
+    total += s;
+    if (lane == 0) {
+      chosen[t * top + k] = where;
+      share[t * top + k] = s;
+      choice[where] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  const float inv = 1.f / (total + mode.share_eps);
+  if (lane < top) share[t * top + lane] *= inv;
+  for (int k = 32 + lane; k < top; k += 32) share[t * top + k] *= inv;
+}
+
 // h [T, width] in T; router float32 [experts, width]; bias float32 [experts] or null.  chosen int32 [T, top], share float32 [T, top].
 // A logit is summed in one order whatever the kernel form: the columns fall into four classes by (c mod 128) / 32; within class k
 // lane l adds the columns 128 i + 32 k + l in order of i, the 32 lanes' sums are added up by the same butterfly, and the four class
@@ -79,15 +165,18 @@ __device__ __forceinline__ void route_choose(float* logits, int* __restrict__ ch
 // classes one after the other.  Shared memory: warps * TOKENS * experts floats.
 template <typename T, int TOKENS>
 __global__ void experts_route_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router, const float* __restrict__ bias,
-                                     int* __restrict__ chosen, float* __restrict__ share, int width, int experts, int top, int num_tokens) {
+                                     int* __restrict__ chosen, float* __restrict__ share, int width, int experts, int top, int num_tokens,
+                                     RouteScored mode) {
   extern __shared__ float logits_all[];
+  const int rows = experts + mode.extra;                                        // rows of the router
+  const int per_token = rows + (mode.on ? experts + mode.groups : 0);           // floats of shared memory a token takes
   grid_dependency_wait();
   allow_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = (blockIdx.x * (blockDim.x >> 5) + warp) * TOKENS;
   if (t0 >= num_tokens) return;
   constexpr int SIDE = 8;   // experts side by side: the tokens' rows are read once per eight experts
-  for (int e0 = 0; e0 < experts; e0 += SIDE) {
+  for (int e0 = 0; e0 < rows; e0 += SIDE) {
     float total[TOKENS][SIDE];
     for (int k = 0; k < 4; ++k) {
       float acc[TOKENS][SIDE];
@@ -101,7 +190,7 @@ __global__ void experts_route_kernel(const T* __restrict__ h, long long ld, cons
 #pragma unroll
         for (int i = 0; i < TOKENS; ++i) x[i] = t0 + i < num_tokens ? to_float<T>(h[(long long)(t0 + i) * ld + c]) : 0.f;
 #pragma unroll
-        for (int j = 0; j < SIDE; ++j) r[j] = e0 + j < experts ? router[(long long)(e0 + j) * width + c] : 0.f;
+        for (int j = 0; j < SIDE; ++j) r[j] = e0 + j < rows ? router[(long long)(e0 + j) * width + c] : 0.f;
 #pragma unroll
         for (int i = 0; i < TOKENS; ++i)
 #pragma unroll
@@ -119,26 +208,32 @@ __global__ void experts_route_kernel(const T* __restrict__ h, long long ld, cons
     for (int i = 0; i < TOKENS; ++i)
 #pragma unroll
       for (int j = 0; j < SIDE; ++j)
-        if (lane == 0 && e0 + j < experts) logits_all[(warp * TOKENS + i) * experts + e0 + j] = total[i][j] + (bias != nullptr ? bias[e0 + j] : 0.f);
+        if (lane == 0 && e0 + j < rows)
+          logits_all[(warp * TOKENS + i) * per_token + e0 + j] = total[i][j] + (bias != nullptr && e0 + j < experts ? bias[e0 + j] : 0.f);
   }
   __syncwarp();
-  for (int i = 0; i < TOKENS && t0 + i < num_tokens; ++i) route_choose(logits_all + (warp * TOKENS + i) * experts, chosen, share, t0 + i, experts, top, lane);
+  for (int i = 0; i < TOKENS && t0 + i < num_tokens; ++i) {
+    float* mine = logits_all + (warp * TOKENS + i) * per_token;
+    if (mode.on) route_choose_scored(mine, mine + rows, mine + rows + experts, chosen, share, t0 + i, experts, top, lane, mode);
+    else route_choose(mine, chosen, share, t0 + i, experts, top, lane);
+  }
 }
 
 // Few tokens: a block of four warps per token, warp k takes class k.  Shared memory: (4 * 8 + experts) floats.
 template <typename T>
 __global__ void __launch_bounds__(128) experts_route_block_kernel(const T* __restrict__ h, long long ld, const float* __restrict__ router,
                                                                   const float* __restrict__ bias, int* __restrict__ chosen, float* __restrict__ share,
-                                                                  int width, int experts, int top) {
+                                                                  int width, int experts, int top, RouteScored mode) {
   extern __shared__ float route_shared[];
   constexpr int SIDE = 8;
   float* parts = route_shared;               // [4][SIDE]
-  float* logits = route_shared + 4 * SIDE;   // [experts]
+  float* logits = route_shared + 4 * SIDE;   // [experts + extra], then with mode.on [experts] choice scores and [groups] groups' worths
+  const int rows = experts + mode.extra;
   grid_dependency_wait();
   allow_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long t = blockIdx.x;
-  for (int e0 = 0; e0 < experts; e0 += SIDE) {
+  for (int e0 = 0; e0 < rows; e0 += SIDE) {
     float acc[SIDE];
 #pragma unroll
     for (int j = 0; j < SIDE; ++j) acc[j] = 0.f;
@@ -146,7 +241,7 @@ __global__ void __launch_bounds__(128) experts_route_block_kernel(const T* __res
     for (int c = threadIdx.x; c < width; c += 128) {
       const float x = to_float<T>(h[t * ld + c]);
 #pragma unroll
-      for (int j = 0; j < SIDE; ++j) acc[j] = fmaf(x, e0 + j < experts ? router[(long long)(e0 + j) * width + c] : 0.f, acc[j]);
+      for (int j = 0; j < SIDE; ++j) acc[j] = fmaf(x, e0 + j < rows ? router[(long long)(e0 + j) * width + c] : 0.f, acc[j]);
     }
 #pragma unroll
     for (int j = 0; j < SIDE; ++j) {
@@ -154,13 +249,16 @@ __global__ void __launch_bounds__(128) experts_route_block_kernel(const T* __res
       if (lane == 0) parts[warp * SIDE + j] = z;
     }
     __syncthreads();
-    if (threadIdx.x < SIDE && e0 + threadIdx.x < experts) {
+    if (threadIdx.x < SIDE && e0 + threadIdx.x < rows) {
       const int j = threadIdx.x;
-      logits[e0 + j] = ((parts[j] + parts[SIDE + j]) + parts[2 * SIDE + j]) + parts[3 * SIDE + j] + (bias != nullptr ? bias[e0 + j] : 0.f);
+      logits[e0 + j] = ((parts[j] + parts[SIDE + j]) + parts[2 * SIDE + j]) + parts[3 * SIDE + j] + (bias != nullptr && e0 + j < experts ? bias[e0 + j] : 0.f);
     }
     __syncthreads();
   }
-  if (warp == 0) route_choose(logits, chosen, share, t, experts, top, lane);
+  if (warp == 0) {
+    if (mode.on) route_choose_scored(logits, logits + rows, logits + rows + experts, chosen, share, t, experts, top, lane, mode);
+    else route_choose(logits, chosen, share, t, experts, top, lane);
+  }
 }
 
 // One block.  chosen [pairs]; slot_of [pairs] out; source [max_slots] out: the pair in a slot, or -1; tile_expert [max_tiles] out:
@@ -206,7 +304,7 @@ template <typename T, bool GLU>
 __global__ void __launch_bounds__(256) experts_product_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ w,
                                                               const int* __restrict__ source, const int* __restrict__ tile_expert,
                                                               int gathered, int divide, void* __restrict__ out_v, int n_out, int k_size,
-                                                              int kind, int interleaved) {
+                                                              int kind, int interleaved, int act_out) {
   constexpr int TN = 64, TK = 16;
   __shared__ float a_tile[EXPERT_ROWS][TK + 1];
   __shared__ float b_tile[GLU ? 2 : 1][TN][TK + 1];
@@ -273,6 +371,7 @@ __global__ void __launch_bounds__(256) experts_product_kernel(const T* __restric
       const int n = n0 + tx * 4 + j;
       if (n >= n_out) continue;
       if (GLU) ((T*)out_v)[slot * n_out + n] = from_float<T>(expert_activation(acc[0][i][j], kind) * acc[GLU ? 1 : 0][i][j]);
+      else if (act_out) ((T*)out_v)[slot * n_out + n] = from_float<T>(expert_activation(acc[0][i][j], kind));   // an ungated expert's first product
       else ((float*)out_v)[slot * n_out + n] = acc[0][i][j];
     }
   }
@@ -298,7 +397,7 @@ template <bool GLU>
 __global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfloat16* __restrict__ a, long long lda,
                                                                   const __nv_bfloat16* __restrict__ w, const int* __restrict__ source,
                                                                   const int* __restrict__ tile_expert, int gathered, int divide,
-                                                                  void* __restrict__ out_v, int n_out, int k_size, int kind, int interleaved) {
+                                                                  void* __restrict__ out_v, int n_out, int k_size, int kind, int interleaved, int act_out) {
   constexpr int TN = MMA_TN, TK = MMA_TK, LD = MMA_TK + MMA_PAD, G = GLU ? 2 : 1, MMA_STAGES = mma_stages(GLU);
   constexpr int A_ELEMENTS = EXPERT_ROWS * LD, STAGE_ELEMENTS = mma_stage_elements(GLU);
   extern __shared__ __align__(16) unsigned char mma_shared[];
@@ -398,15 +497,18 @@ __global__ void __launch_bounds__(128) experts_product_mma_kernel(const __nv_bfl
           if (n >= n_out) continue;
           const float value = acc[0][i][j][2 * half + e];
           if (GLU) ((__nv_bfloat16*)out_v)[slot * n_out + n] = __float2bfloat16_rn(expert_activation(value, kind) * acc[G - 1][i][j][2 * half + e]);
+          else if (act_out) ((__nv_bfloat16*)out_v)[slot * n_out + n] = __float2bfloat16_rn(expert_activation(value, kind));
           else ((float*)out_v)[slot * n_out + n] = value;
         }
     }
 }
 
 // out[t, c] = sum_k share[t, k] * y[slot_of[t * top + k], c], the choices in their order; y in float32 or in the compute dtype.
-template <typename Y>
+// With `common` ([T, width] in C, an expert that every token goes through) and `gate` (float32 [T]): + gate[t] * common[t, c].
+template <typename Y, typename C>
 __global__ void experts_gather_kernel(const Y* __restrict__ y, const int* __restrict__ slot_of, const float* __restrict__ share,
-                                      float* __restrict__ out, int width, int top, long long total) {
+                                      float* __restrict__ out, int width, int top, long long total, const C* __restrict__ common,
+                                      const float* __restrict__ gate) {
   grid_dependency_wait();
   allow_dependents();
   const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -415,6 +517,7 @@ __global__ void experts_gather_kernel(const Y* __restrict__ y, const int* __rest
   const int c = (int)(item % width);
   float acc = 0.f;
   for (int k = 0; k < top; ++k) acc = fmaf(share[t * top + k], to_float<Y>(y[(long long)slot_of[t * top + k] * width + c]), acc);
+  if (common != nullptr) acc = fmaf(gate[t], to_float<C>(common[item]), acc);
   out[item] = acc;
 }
 
@@ -438,25 +541,33 @@ using namespace pylon;
 
 extern "C" int pylon_experts_row_tile() { return EXPERT_ROWS; }
 
+// scored != 0: the sigmoid form (see RouteScored); router is then float32 [experts + extra, width].
 extern "C" int pylon_experts_route(const void* h, long long ld, const float* router, const float* bias, int* chosen, float* share, int width,
-                                   int experts, int top, int num_tokens, int dtype, cudaStream_t stream) {
+                                   int experts, int top, int num_tokens, int dtype, int scored, const float* correction, int groups, int keep,
+                                   float share_eps, int extra, float* extra_out, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > experts || experts > 2048) PYLON_REFUSE("experts_route: %d of %d experts (at most 2048)", top, experts);
+  if (!scored && (correction || groups || extra)) PYLON_REFUSE("experts_route: a correction, groups and extra rows go with the sigmoid form");
+  if (scored && (groups < 0 || (groups > 0 && (experts % groups || keep < 1 || keep > groups || top > keep * (experts / groups))) || extra < 0 || extra > 64 ||
+                 (extra > 0 && !extra_out)))
+    PYLON_REFUSE("experts_route: %d groups of which %d are kept for %d of %d experts, %d extra rows", groups, keep, top, experts, extra);
+  const RouteScored mode{scored ? 1 : 0, correction, groups, keep, share_eps, extra, extra_out};
+  const int per_token = experts + extra + (scored ? experts + groups : 0);
   if (num_tokens < 512) {   // a step of few tokens wants many threads a token
-    const size_t smem = (size_t)(4 * 8 + experts) * sizeof(float);
+    const size_t smem = (size_t)(4 * 8 + per_token) * sizeof(float);
     if (dtype == PYLON_DTYPE_F32)
-      launch_dependent(experts_route_block_kernel<float>, dim3((unsigned)num_tokens), dim3(128), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top);
+      launch_dependent(experts_route_block_kernel<float>, dim3((unsigned)num_tokens), dim3(128), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top, mode);
     else if (dtype == PYLON_DTYPE_BF16)
-      launch_dependent(experts_route_block_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(128), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top);
+      launch_dependent(experts_route_block_kernel<__nv_bfloat16>, dim3((unsigned)num_tokens), dim3(128), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top, mode);
     else PYLON_REFUSE("experts_route: unknown dtype %d", dtype);
   } else {
     constexpr int warps = 4, side = 4;   // tokens a warp takes side by side (57 us for 2,048 tokens of 2,048 columns and 8 experts; two a warp took 73 us)
     const dim3 grid((unsigned)((num_tokens + warps * side - 1) / (warps * side)));
-    const size_t smem = (size_t)warps * side * experts * sizeof(float);
+    const size_t smem = (size_t)warps * side * per_token * sizeof(float);
     if (dtype == PYLON_DTYPE_F32)
-      launch_dependent(experts_route_kernel<float, side>, grid, dim3(warps * 32), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
+      launch_dependent(experts_route_kernel<float, side>, grid, dim3(warps * 32), smem, stream, (const float*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens, mode);
     else if (dtype == PYLON_DTYPE_BF16)
-      launch_dependent(experts_route_kernel<__nv_bfloat16, side>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens);
+      launch_dependent(experts_route_kernel<__nv_bfloat16, side>, grid, dim3(warps * 32), smem, stream, (const __nv_bfloat16*)h, ld, router, bias, chosen, share, width, experts, top, num_tokens, mode);
     else PYLON_REFUSE("experts_route: unknown dtype %d", dtype);
   }
   PYLON_CHECK_LAUNCH("experts_route");
@@ -484,17 +595,20 @@ static void allow_mma_shared_memory() {
 
 // a: [rows, lda] in dtype; w: [experts, (glu ? 2 : 1) * n_out, k] in dtype, contiguous (with glu an expert's gate rows, then its up rows;
 // or, interleaved != 0, alternating in groups of 8); out: [max_tiles * EXPERT_ROWS, n_out], in dtype with glu, else float32.
+// glu == 2: no gate, but the activation on the product itself, out in dtype (the first product of an ungated expert).
 extern "C" int pylon_experts_product(const void* a, long long lda, const void* w, const int* source, const int* tile_expert, int gathered,
                                      int divide, void* out, int n_out, int k_size, int max_tiles, int glu, int kind, int interleaved, int dtype,
                                      cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
-  if (n_out <= 0 || k_size <= 0 || divide < 1 || kind < 0 || kind > 2) PYLON_REFUSE("experts_product: n %d, k %d, divide %d, activation %d", n_out, k_size, divide, kind);
+  const int act_out = glu == 2 ? 1 : 0;
+  if (act_out) glu = 0;
+  if (n_out <= 0 || k_size <= 0 || divide < 1 || kind < 0 || kind > 3) PYLON_REFUSE("experts_product: n %d, k %d, divide %d, activation %d", n_out, k_size, divide, kind);
   if (max_tiles > 65535) PYLON_REFUSE("experts_product: %d row tiles", max_tiles);
   if (interleaved && (!glu || n_out % 8)) PYLON_REFUSE("experts_product: interleaved rows need a gated product of a multiple of 8 columns, got %d", n_out);
   const dim3 grid((unsigned)((n_out + 63) / 64), (unsigned)max_tiles);
   if (dtype == PYLON_DTYPE_F32) {
-    if (glu) launch_dependent(experts_product_kernel<float, true>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
-    else launch_dependent(experts_product_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+    if (glu) launch_dependent(experts_product_kernel<float, true>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved, act_out);
+    else launch_dependent(experts_product_kernel<float, false>, grid, dim3(256), 0, stream, (const float*)a, lda, (const float*)w, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved, act_out);
   } else if (dtype == PYLON_DTYPE_BF16) {
     const __nv_bfloat16* ab = (const __nv_bfloat16*)a;
     const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
@@ -502,14 +616,14 @@ extern "C" int pylon_experts_product(const void* a, long long lda, const void* w
     if (vectors) {
       if (glu) {
         allow_mma_shared_memory<true>();
-        launch_dependent(experts_product_mma_kernel<true>, grid, dim3(128), mma_shared_bytes(true), stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+        launch_dependent(experts_product_mma_kernel<true>, grid, dim3(128), mma_shared_bytes(true), stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved, act_out);
       } else {
         allow_mma_shared_memory<false>();
-        launch_dependent(experts_product_mma_kernel<false>, grid, dim3(128), mma_shared_bytes(false), stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+        launch_dependent(experts_product_mma_kernel<false>, grid, dim3(128), mma_shared_bytes(false), stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved, act_out);
       }
     } else {
-      if (glu) launch_dependent(experts_product_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
-      else launch_dependent(experts_product_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved);
+      if (glu) launch_dependent(experts_product_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved, act_out);
+      else launch_dependent(experts_product_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, ab, lda, wb, source, tile_expert, gathered, divide, out, n_out, k_size, kind, interleaved, act_out);
     }
   } else PYLON_REFUSE("experts_product: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("experts_product");
@@ -530,13 +644,18 @@ extern "C" int pylon_experts_sort_rows(const void* h, long long ld, const int* s
 }
 
 // y: [slots, width] in float32 (y_dtype PYLON_DTYPE_F32) or bfloat16; out float32 [num_tokens, width].
+// common ([num_tokens, width] in common_dtype) and gate (float32 [num_tokens]), both or neither: out += gate[t] * common[t].
 extern "C" int pylon_experts_gather(const void* y, const int* slot_of, const float* share, float* out, int num_tokens, int width, int top, int y_dtype,
-                                    cudaStream_t stream) {
+                                    const void* common, const float* gate, int common_dtype, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
+  if ((common == nullptr) != (gate == nullptr)) PYLON_REFUSE("experts_gather: a common expert's output and its gate go together");
   const long long total = (long long)num_tokens * width;
   const dim3 grid((unsigned)((total + 255) / 256));
-  if (y_dtype == PYLON_DTYPE_F32) launch_dependent(experts_gather_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, slot_of, share, out, width, top, total);
-  else if (y_dtype == PYLON_DTYPE_BF16) launch_dependent(experts_gather_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)y, slot_of, share, out, width, top, total);
+  const bool common_f32 = common == nullptr || common_dtype == PYLON_DTYPE_F32;
+#define PYLON_GATHER(Y, C) launch_dependent(experts_gather_kernel<Y, C>, grid, dim3(256), 0, stream, (const Y*)y, slot_of, share, out, width, top, total, (const C*)common, gate)
+  if (y_dtype == PYLON_DTYPE_F32) { if (common_f32) PYLON_GATHER(float, float); else PYLON_GATHER(float, __nv_bfloat16); }
+  else if (y_dtype == PYLON_DTYPE_BF16) { if (common_f32) PYLON_GATHER(__nv_bfloat16, float); else PYLON_GATHER(__nv_bfloat16, __nv_bfloat16); }
   else PYLON_REFUSE("experts_gather: unknown dtype %d", y_dtype);
+#undef PYLON_GATHER
   PYLON_CHECK_LAUNCH("experts_gather");
 }

@@ -1,0 +1,189 @@
+// A matrix of memory per head with exponential gates (the mLSTM cell of xLSTM), walked token by token.
+//
+// Per token and head, from one product of the layer's input, columns [q | k | v | g] (q, k: heads x dim; v, g: heads x vdim), and
+// float32 gate logits [i | f] (heads each) with biases:
+//
+//     q = q * dim^-1/2
+//     i = cap * tanh((i + b_i) / cap)                      the log of the input gate
+//     f = logsigmoid(cap * tanh((f + b_f) / cap))          the log of the forget gate
+//     m' = max(f + m, i)                                   a running maximum that starts at 0
+//     S = exp(f + m - m') S + exp(i - m') k v^T            S [dim, vdim] and n [dim] start at zero
+//     n = exp(f + m - m') n + exp(i - m') k
+//     o = S^T q / (max(|n . q|, exp(-m')) + read_eps)
+//
+// and then, in a second kernel, each head's o divided by its root mean square (eps inside the root), times a weight [heads * vdim],
+// times sigmoid(g), in the compute dtype: ready for the output projection.
+//
+// What a request carries from token to token is one float32 slot, per head [S (dim x vdim) | n (dim) | m].  The columns of S do not
+// see each other, so a block takes (request row, head, 32 columns): warp w of four owns eight neighbouring columns, lane l the rows
+// l, l + 32, ... of them (up to MEMORY_MAX_DIM rows), and a read-out is a sum over the lanes.  n and m are kept by every warp (the
+// same arithmetic in the same order); the first warp leaves their new values in a buffer beside the state, and a small kernel behind
+// the walk puts them into the slot (a block that starts late must still find the old ones there).  Everything is float32.
+#include "common.cuh"
+
+namespace pylon {
+
+constexpr int MEMORY_COLUMNS = 8;        // columns of S a warp owns
+constexpr int MEMORY_WARPS = 4;
+constexpr int MEMORY_MAX_DIM = 256;      // rows of S: up to 8 a lane
+
+__device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+template <typename T, int PER_LANE>
+__global__ void __launch_bounds__(MEMORY_WARPS * 32) matrix_memory_scan_kernel(
+    const T* __restrict__ proj, long long ld, const float* __restrict__ gate_logits, const float* __restrict__ bias_i, const float* __restrict__ bias_f,
+    float cap, float read_eps, float* __restrict__ state, long long state_floats, const int* __restrict__ q_start, const int* __restrict__ slots,
+    float* __restrict__ read, float* __restrict__ fresh, int heads, int dim, int vdim) {
+  grid_dependency_wait();
+  allow_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y, row = blockIdx.z;
+  const int j0 = (blockIdx.x * MEMORY_WARPS + warp) * MEMORY_COLUMNS;
+  const int first = q_start[row], count = q_start[row + 1] - first;
+  if (count <= 0 || j0 >= vdim) return;   // a row without tokens (a padded step) keeps its state; a warp beyond the last column has nothing
+  float* mine = state + (long long)slots[row] * state_floats + (long long)head * ((long long)dim * vdim + dim + 1);
+  float* n_state = mine + (long long)dim * vdim;
+  float s[PER_LANE][MEMORY_COLUMNS], n[PER_LANE];
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int d = lane + 32 * i;
+    n[i] = d < dim ? n_state[d] : 0.f;
+#pragma unroll
+    for (int c = 0; c < MEMORY_COLUMNS; ++c) s[i][c] = (d < dim && j0 + c < vdim) ? mine[(long long)d * vdim + j0 + c] : 0.f;
+  }
+  float m = n_state[dim];
+  const float bi = bias_i[head], bf = bias_f[head];
+  const float q_scale = rsqrtf((float)dim);
+  const long long q_column = (long long)head * dim, k_column = (long long)heads * dim + q_column;
+  const long long v_column = 2LL * heads * dim + (long long)head * vdim + j0;
+  for (int t = first; t < first + count; ++t) {
+    const T* x = proj + (long long)t * ld;
+    const float gi = cap * tanhf((gate_logits[(long long)t * 2 * heads + head] + bi) / cap);
+    const float gf = log_sigmoid_f(cap * tanhf((gate_logits[(long long)t * 2 * heads + heads + head] + bf) / cap));
+    const float m_new = fmaxf(gf + m, gi);
+    const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
+    m = m_new;
+    float v[MEMORY_COLUMNS], o[MEMORY_COLUMNS];
+#pragma unroll
+    for (int c = 0; c < MEMORY_COLUMNS; ++c) {
+      v[c] = j0 + c < vdim ? to_float<T>(x[v_column + c]) : 0.f;
+      o[c] = 0.f;
+    }
+    float nq = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      const float k = d < dim ? to_float<T>(x[k_column + d]) * take : 0.f;
+      const float q = d < dim ? to_float<T>(x[q_column + d]) * q_scale : 0.f;
+      n[i] = fmaf(keep, n[i], k);
+      nq = fmaf(n[i], q, nq);
+#pragma unroll
+      for (int c = 0; c < MEMORY_COLUMNS; ++c) {
+        s[i][c] = fmaf(keep, s[i][c], k * v[c]);
+        o[c] = fmaf(s[i][c], q, o[c]);
+      }
+    }
+    nq = warp_sum(nq);
+    const float below = fmaxf(fabsf(nq), expf(-m)) + read_eps;
+    float result = 0.f;
+#pragma unroll
+    for (int c = 0; c < MEMORY_COLUMNS; ++c) {
+      const float sum = warp_sum(o[c]);
+      if (lane == c) result = sum;
+    }
+    if (lane < MEMORY_COLUMNS && j0 + lane < vdim) read[(long long)t * heads * vdim + (long long)head * vdim + j0 + lane] = result / below;
+  }
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int d = lane + 32 * i;
+    if (d >= dim) continue;
+    if (j0 == 0) fresh[((long long)row * heads + head) * (dim + 1) + d] = n[i];
+#pragma unroll
+    for (int c = 0; c < MEMORY_COLUMNS; ++c)
+      if (j0 + c < vdim) mine[(long long)d * vdim + j0 + c] = s[i][c];
+  }
+  if (j0 == 0 && lane == 0) fresh[((long long)row * heads + head) * (dim + 1) + dim] = m;
+}
+
+// fresh [rows, heads, dim + 1] -> the n and m of every head in the rows' slots; rows without tokens keep theirs.
+__global__ void matrix_memory_commit_kernel(const float* __restrict__ fresh, float* __restrict__ state, long long state_floats, const int* __restrict__ q_start,
+                                            const int* __restrict__ slots, int heads, int dim, int vdim) {
+  grid_dependency_wait();
+  allow_dependents();
+  const int head = blockIdx.x, row = blockIdx.y;
+  if (q_start[row + 1] - q_start[row] <= 0) return;
+  float* n_state = state + (long long)slots[row] * state_floats + (long long)head * ((long long)dim * vdim + dim + 1) + (long long)dim * vdim;
+  const float* from = fresh + ((long long)row * heads + head) * (dim + 1);
+  for (int e = threadIdx.x; e <= dim; e += blockDim.x) n_state[e] = from[e];
+}
+
+// One warp per (token, head): read [T, heads * vdim] float32 -> out in T = read / rms(read over the head) * weight * sigmoid(g).
+template <typename T>
+__global__ void matrix_memory_out_kernel(const float* __restrict__ read, const T* __restrict__ proj, long long ld, long long g_column,
+                                         const float* __restrict__ weight, float eps, T* __restrict__ out, int heads, int vdim, long long items) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const long long t = item / heads;
+  const int head = (int)(item % heads);
+  const float* o = read + t * heads * vdim + (long long)head * vdim;
+  float squares = 0.f;
+  for (int j = lane; j < vdim; j += 32) squares = fmaf(o[j], o[j], squares);
+  const float inv = rsqrtf(warp_sum(squares) / (float)vdim + eps);
+  const T* g = proj + t * ld + g_column + (long long)head * vdim;
+  T* dst = out + t * heads * vdim + (long long)head * vdim;
+  for (int j = lane; j < vdim; j += 32) dst[j] = from_float<T>(o[j] * inv * weight[head * vdim + j] / (1.f + expf(-to_float<T>(g[j]))));
+}
+
+}  // namespace pylon
+
+using namespace pylon;
+
+// proj [T, ld] in dtype, columns [q | k | v | g]; gate_logits float32 [T, 2 heads]; state float32 [slots, state_floats]; read float32
+// [T, heads * vdim] out; fresh float32 [num_rows, heads, dim + 1]: scratch.
+extern "C" int pylon_matrix_memory_scan(const void* proj, long long ld, const float* gate_logits, const float* bias_i, const float* bias_f, float cap,
+                                        float read_eps, float* state, long long state_floats, const int* q_start, const int* slots, float* read, float* fresh,
+                                        int heads, int dim, int vdim, int num_rows, int dtype, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (heads < 1 || dim < 1 || dim > MEMORY_MAX_DIM || vdim < 1 || !(cap > 0.f) || num_rows > 65535 || heads > 65535 ||
+      state_floats < (long long)heads * ((long long)dim * vdim + dim + 1))
+    PYLON_REFUSE("matrix_memory_scan: %d heads of %d x %d (at most %d rows), cap %f, %d request rows", heads, dim, vdim, MEMORY_MAX_DIM, cap, num_rows);
+  const int per_block = MEMORY_WARPS * MEMORY_COLUMNS;
+  const dim3 grid((unsigned)((vdim + per_block - 1) / per_block), (unsigned)heads, (unsigned)num_rows);
+  const dim3 block(MEMORY_WARPS * 32);
+  const int per_lane = (dim + 31) / 32;
+#define PYLON_MEMORY(T, P)                                                                                                                          \
+  launch_dependent(matrix_memory_scan_kernel<T, P>, grid, block, 0, stream, (const T*)proj, ld, gate_logits, bias_i, bias_f, cap, read_eps, state, \
+                   state_floats, q_start, slots, read, fresh, heads, dim, vdim)
+#define PYLON_MEMORY_T(T)                                                                          \
+  do {                                                                                             \
+    if (per_lane <= 1) PYLON_MEMORY(T, 1); else if (per_lane <= 2) PYLON_MEMORY(T, 2);             \
+    else if (per_lane <= 4) PYLON_MEMORY(T, 4); else PYLON_MEMORY(T, 8);                           \
+  } while (0)
+  if (dtype == PYLON_DTYPE_F32) PYLON_MEMORY_T(float);
+  else if (dtype == PYLON_DTYPE_BF16) PYLON_MEMORY_T(__nv_bfloat16);
+  else PYLON_REFUSE("matrix_memory_scan: unknown dtype %d", dtype);
+#undef PYLON_MEMORY_T
+#undef PYLON_MEMORY
+  launch_dependent(matrix_memory_commit_kernel, dim3((unsigned)heads, (unsigned)num_rows), dim3(64), 0, stream, (const float*)fresh, state, state_floats, q_start,
+                   slots, heads, dim, vdim);
+  PYLON_CHECK_LAUNCH("matrix_memory_scan");
+}
+
+extern "C" int pylon_matrix_memory_out(const float* read, const void* proj, long long ld, long long g_column, const float* weight, float eps, void* out,
+                                       int heads, int vdim, int num_tokens, int dtype, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (heads < 1 || vdim < 1) PYLON_REFUSE("matrix_memory_out: %d heads of %d", heads, vdim);
+  const long long items = (long long)num_tokens * heads;
+  const int warps = 4;
+  const dim3 grid((unsigned)((items + warps - 1) / warps));
+  if (dtype == PYLON_DTYPE_F32)
+    launch_dependent(matrix_memory_out_kernel<float>, grid, dim3(warps * 32), 0, stream, read, (const float*)proj, ld, g_column, weight, eps, (float*)out, heads, vdim, items);
+  else if (dtype == PYLON_DTYPE_BF16)
+    launch_dependent(matrix_memory_out_kernel<__nv_bfloat16>, grid, dim3(warps * 32), 0, stream, read, (const __nv_bfloat16*)proj, ld, g_column, weight, eps,
+                     (__nv_bfloat16*)out, heads, vdim, items);
+  else PYLON_REFUSE("matrix_memory_out: unknown dtype %d", dtype);
+  PYLON_CHECK_LAUNCH("matrix_memory_out");
+}

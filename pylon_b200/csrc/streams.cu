@@ -14,7 +14,8 @@
 //
 // Norm kinds: 0 = layer norm without bias, (u - mean) / sqrt(var + eps) * w with var the mean of
 // the squared deviations (two passes over the row, which lies in shared memory); 1 = RMS norm,
-// u / sqrt(mean(u^2) + eps) * w.  Everything is float32 but the sublayer's output as it comes in
+// u / sqrt(mean(u^2) + eps) * w; 2 = dynamic tanh, tanh(alpha u) * w + b with alpha one learnt number and b a
+// vector (no statistics of the row, no eps).  Everything is float32 but the sublayer's output as it comes in
 // and the normalised row as it goes out.  With a row selection the streams are not written: the
 // selected rows are normalised from the updated values computed on the fly (final norm at the
 // rows whose logits are wanted).
@@ -44,7 +45,8 @@ template <typename TD, typename TO, int V>
 __global__ void streams_update_norm_kernel(float* __restrict__ x, const TD* __restrict__ delta, int delta_parts, long long part_stride,
                                            float scale, const float* __restrict__ mix, const float* __restrict__ outw,
                                            const float* __restrict__ read, const float* __restrict__ weight, const int* __restrict__ rows,
-                                           TO* __restrict__ out, int streams, int width, float eps, int kind) {
+                                           TO* __restrict__ out, int streams, int width, float eps, int kind,
+                                           const float* __restrict__ bias, const float* __restrict__ alpha) {
   extern __shared__ __align__(16) float shared[];
   float* u_row = shared;                 // [width]
   float* scratch = u_row + width;        // [34]
@@ -130,22 +132,26 @@ __global__ void streams_update_norm_kernel(float* __restrict__ x, const TD* __re
     }
   }
   if (!out) return;
-  float mean = 0.f;
+  float mean = 0.f, inv = 1.f;
   if (kind == 0) mean = block_sum(local_sum, scratch) / (float)width;
-  float local_sq = 0.f;
-  for (int e = threadIdx.x * V; e < width; e += blockDim.x * V) {   // each thread reads back what it wrote itself
+  if (kind != 2) {
+    float local_sq = 0.f;
+    for (int e = threadIdx.x * V; e < width; e += blockDim.x * V) {   // each thread reads back what it wrote itself
 #pragma unroll
-    for (int v = 0; v < V; ++v) {
-      const float c = u_row[e + v] - mean;
-      local_sq = fmaf(c, c, local_sq);
+      for (int v = 0; v < V; ++v) {
+        const float c = u_row[e + v] - mean;
+        local_sq = fmaf(c, c, local_sq);
+      }
     }
+    inv = rsqrtf(block_sum(local_sq, scratch) / (float)width + eps);
   }
-  const float inv = rsqrtf(block_sum(local_sq, scratch) / (float)width + eps);
+  const float slope = kind == 2 ? alpha[0] : 0.f;
   TO* orow = out + (long long)n * width;
   for (int e = threadIdx.x * V; e < width; e += blockDim.x * V) {
     float result[V];
 #pragma unroll
-    for (int v = 0; v < V; ++v) result[v] = (u_row[e + v] - mean) * inv * weight[e + v];
+    for (int v = 0; v < V; ++v)
+      result[v] = kind == 2 ? fmaf(tanhf(slope * u_row[e + v]), weight[e + v], bias[e + v]) : (u_row[e + v] - mean) * inv * weight[e + v];
     if constexpr (V == 4 && sizeof(TO) == 2) {
       const __nv_bfloat162 a = __floats2bfloat162_rn(result[0], result[1]), b = __floats2bfloat162_rn(result[2], result[3]);
       uint2 packed;
@@ -171,11 +177,12 @@ using namespace pylon;
 extern "C" int pylon_streams_update_norm(float* x, const void* delta, int delta_parts, int delta_dtype, float scale, const float* mix,
                                          const float* outw, const float* read, const float* weight, const int* rows, void* out,
                                          int out_dtype, int n_rows, int tokens, int streams, int width, float eps, int kind,
-                                         cudaStream_t stream) {
+                                         const float* bias, const float* alpha, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (streams < 1 || streams > MAX_STREAMS) PYLON_REFUSE("streams_update_norm: %d streams (1 to %d)", streams, MAX_STREAMS);
   if (width < 1 || width > 32768) PYLON_REFUSE("streams_update_norm: width %d", width);
-  if (kind != 0 && kind != 1) PYLON_REFUSE("streams_update_norm: norm kind %d", kind);
+  if (kind < 0 || kind > 2) PYLON_REFUSE("streams_update_norm: norm kind %d", kind);
+  if (kind == 2 && out && (!bias || !alpha)) PYLON_REFUSE("streams_update_norm: a dynamic tanh needs its bias and its alpha");
   if ((weight == nullptr) != (out == nullptr)) PYLON_REFUSE("streams_update_norm: a norm weight and an output go together");
   if (!out && rows) PYLON_REFUSE("streams_update_norm: a row selection without an output does nothing");
   if (delta && delta_parts < 1) PYLON_REFUSE("streams_update_norm: %d parts", delta_parts);
@@ -199,7 +206,8 @@ extern "C" int pylon_streams_update_norm(float* x, const void* delta, int delta_
       raised[current_device_slot()] = true;                                                                                      \
     }                                                                                                                            \
     launch_dependent(streams_update_norm_kernel<TD, TO, V>, dim3(n_rows), dim3(threads), smem, stream, x, (const TD*)delta,      \
-                     delta_parts, part_stride, scale, mix, outw, read, weight, rows, (TO*)out, streams, width, eps, kind);       \
+                     delta_parts, part_stride, scale, mix, outw, read, weight, rows, (TO*)out, streams, width, eps, kind, bias,  \
+                     alpha);                                                                                                     \
   } while (0)
 #define PYLON_STREAMS_LAUNCH(TD, TO)                                                      \
   do {                                                                                    \

@@ -180,10 +180,12 @@ _SIGNATURES = {
         "pylon_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
         "pylon_qk_norm_mix_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+        "pylon_qk_whole_norm_kv_write": [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     },
     "streams.cu": {
         "pylon_streams_update_norm": [c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                                      c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p],
     },
     "delta_rule.cu": {
         "pylon_gated_delta_rule": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -195,20 +197,34 @@ _SIGNATURES = {
                               c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
                               c_int, c_void_p],
     },
+    "linear_recurrence.cu": {
+        "pylon_linear_recurrence_conv": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "pylon_linear_recurrence_scan": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                         c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "matrix_memory.cu": {
+        "pylon_matrix_memory_scan": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_matrix_memory_out": [c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
     "combine.cu": {
         "pylon_side_by_side": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "pylon_gated_unit": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_add_bias": [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
         "pylon_mean_of_normed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+        "pylon_weighted_sum": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
+        "pylon_activation": [c_void_p, c_longlong, c_int, c_int, c_void_p],
     },
     "experts.cu": {
         "pylon_experts_row_tile": [],
-        "pylon_experts_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_experts_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                c_float, c_int, c_void_p, c_void_p],
         "pylon_experts_plan": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_experts_product": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p],
         "pylon_experts_sort_rows": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-        "pylon_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "pylon_experts_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     },
     "gemm_f32.cu": {
         "pylon_gemm_f32_nt": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p],
@@ -257,7 +273,7 @@ _SIGNATURES = {
     "attention_simple.cu": {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-                                         c_void_p, c_longlong, c_longlong, c_int, c_int, c_void_p],
+                                         c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     },
     "attention_mma.cu": {
         "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -844,8 +860,14 @@ def paged_attention(
     softcap: Optional[float] = None,
     sinks: Optional[torch.Tensor] = None,
     values_in_keys: Optional[int] = None,
+    keep_first: int = 0,
+    distance_bias: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
+
+    ``keep_first`` n: a window never hides the keys at positions below n (a token sees ``j <= p`` with ``p - j < window`` or
+    ``j < n``).  ``distance_bias``: float32 ``[rows, nq]``; the scaled score of the key ``p - j`` positions back gets
+    ``distance_bias[min(p - j, rows - 1), h]`` added.  Both run on the plain kernel.
 
     ``sinks``: float32 ``[nq]``; the softmax's denominator of head h also holds ``exp(sinks[h])``, a key without a
     value whose score is taken as it stands.  ``values_in_keys`` n (with ``v_pages=None``): the values are the first n
@@ -878,8 +900,13 @@ def paged_attention(
     else on ``mma.sync``; decoded tokens on their own kernel.  float32, and other head sizes up
     to 512, take the plain kernel.
     """
-    _need_cuda(q, k_pages, v_pages, positions, token_row, q_start, kv_len, block_table, out, sinks)
+    _need_cuda(q, k_pages, v_pages, positions, token_row, q_start, kv_len, block_table, out, sinks, distance_bias)
     _need(sinks is None or (sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous()), "paged_attention: sinks must be float32 [nq]")
+    _need(distance_bias is None or (distance_bias.dtype == torch.float32 and distance_bias.dim() == 2 and distance_bias.shape[0] >= 1 and distance_bias.shape[1] == nq
+                                    and distance_bias.is_contiguous()), "paged_attention: distance_bias must be contiguous float32 [rows, nq]")
+    _need(keep_first >= 0 and (keep_first == 0 or (chunk is None and values_in_keys is None)), "paged_attention: kept first keys go with a window only")
+    _need(distance_bias is None or values_in_keys is None, "paged_attention: no bias by distance over latent rows")
+    plain_only = keep_first > 0 or distance_bias is not None
     if values_in_keys is not None:
         _need(v_pages is None and k_pages.dim() == 4 and k_pages.is_contiguous() and 1 <= values_in_keys <= k_pages.shape[3],
               "paged_attention: values inside the key rows are their first columns, and there are no value pages then")
@@ -906,7 +933,7 @@ def paged_attention(
     _need(out.shape == (tokens, nq * dv) and out.dtype == q.dtype and out.is_contiguous(), "paged_attention: out has the wrong shape or dtype")
     scale = 1.0 / math.sqrt(d) if scale is None else float(scale)
     _need(scale > 0, "paged_attention: the softmax scale must be positive")
-    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple and same_width and sinks is None:
+    if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and not force_simple and same_width and sinks is None and not plain_only:
         library = _library("attention_mma.cu", {"PYLON_HEAD_DIM": d})
         group = nq // nkv
         any_large = max_q * group > 16
@@ -956,7 +983,7 @@ def paged_attention(
     _check(library, library.pylon_paged_attention_simple(
         _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),
         block_table.shape[1], page_size, num_pages, nq, nkv, d, dv, int(window or 0), int(chunk or 0), float(softcap or 0.0), scale,
-        _ptr(sinks), 0, 0, tokens, _dtype_code(q.dtype), _stream()))
+        _ptr(sinks), 0, 0, tokens, _dtype_code(q.dtype), int(keep_first), _ptr(distance_bias), 0 if distance_bias is None else distance_bias.shape[0], _stream()))
     return out
 
 
@@ -1004,7 +1031,7 @@ def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block
     _check(library, library.pylon_paged_attention_simple(
         _ptr(q), q.stride(0), _ptr(pages), _ptr(pages), _ptr(out), _ptr(positions), _ptr(token_row), _ptr(block_table),
         block_table.shape[1], page_size, num_pages, nq, 1, d, dv, int(window or 0), 0, 0.0, float(scale),
-        _ptr(sinks), d, d, tokens, _dtype_code(q.dtype), _stream()))
+        _ptr(sinks), d, d, tokens, _dtype_code(q.dtype), 0, None, 0, _stream()))
     return out
 
 
@@ -1026,6 +1053,7 @@ def qk_norm_mix_kv_write(
     other_values: Optional[torch.Tensor] = None,
     mix_weight: Optional[torch.Tensor] = None,
     other_head_width: Optional[int] = None,
+    whole_rows: bool = False,
 ) -> torch.Tensor:
     """For attention without rotation, on ``qkv [T, nq * d + nkv * d + nkv * dv]``: RMSNorm each q and k head (when
     weights are given), q back in place, k into its page slot; every v head, mixed first with another layer's values
@@ -1037,9 +1065,11 @@ def qk_norm_mix_kv_write(
     _need_cuda(qkv, q_weight, k_weight, positions, token_row, block_table, k_pages, v_pages, other_values, mix_weight)
     tokens = qkv.shape[0]
     _need(qkv.dim() == 2 and qkv.is_contiguous() and qkv.shape[1] == (nq + nkv) * head_dim + nkv * value_dim, "qk_norm_mix_kv_write: qkv must be contiguous [T, nq d + nkv d + nkv dv]")
-    for weight in (q_weight, k_weight):
-        if weight is not None:
-            _need(weight.dtype == torch.float32 and weight.shape == (head_dim,) and weight.is_contiguous(), "qk_norm_mix_kv_write: norm weights must be float32 [d]")
+    for weight, heads in ((q_weight, nq), (k_weight, nkv)):
+        if weight is not None or whole_rows:
+            size = heads * head_dim if whole_rows else head_dim
+            _need(weight is not None and weight.dtype == torch.float32 and weight.shape == (size,) and weight.is_contiguous(),
+                  f"qk_norm_mix_kv_write: norm weights must be float32 [{size}]")
     for meta in (positions, token_row):
         _need(meta.dtype == torch.int32 and meta.is_contiguous() and meta.shape[0] >= tokens, "qk_norm_mix_kv_write: positions/token_row must be int32 [T]")
     _need(block_table.dtype == torch.int32 and block_table.dim() == 2 and block_table.is_contiguous(), "qk_norm_mix_kv_write: block_table must be contiguous int32 [rows, width]")
@@ -1056,6 +1086,13 @@ def qk_norm_mix_kv_write(
         _need(mix_weight.dtype == torch.float32 and mix_weight.numel() == 1, "qk_norm_mix_kv_write: the mixing weight is one float32")
         other_stride = other_values.stride(0)
     library = _library("elementwise.cu")
+    if whole_rows:
+        _need(other_values is None, "qk_norm_mix_kv_write: no value mixing beside norms over whole rows")
+        _check(library, library.pylon_qk_whole_norm_kv_write(
+            _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(positions), _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size,
+            _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], nq, nkv, head_dim, value_dim, tokens, _dtype_code(qkv.dtype),
+            _ptr(cache_write_error_word(k_pages.device)), _stream()))
+        return qkv
     _check(library, library.pylon_qk_norm_mix_kv_write(
         _ptr(qkv), _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(other_values), other_stride, other_head_width, _ptr(mix_weight), _ptr(positions),
         _ptr(token_row), _ptr(block_table), block_table.shape[1], page_size, _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], nq, nkv,
@@ -1066,7 +1103,7 @@ def qk_norm_mix_kv_write(
 # ---------------------------------------------------------------------------------------
 # residual streams (one or several) and the norms that read them
 # ---------------------------------------------------------------------------------------
-NORM_KINDS = {"layernorm": 0, "rmsnorm": 1}
+NORM_KINDS = {"layernorm": 0, "rmsnorm": 1, "dynamic_tanh": 2}
 
 
 def streams_update_norm(
@@ -1081,6 +1118,8 @@ def streams_update_norm(
     kind: str = "layernorm",
     out_dtype: Optional[torch.dtype] = None,
     rows: Optional[torch.Tensor] = None,
+    norm_bias: Optional[torch.Tensor] = None,
+    norm_alpha: Optional[torch.Tensor] = None,
 ) -> Optional[torch.Tensor]:
     """The residual stream kept as ``S`` copies, float32 ``[T, S, width]`` (``[T, width]`` is one copy).
 
@@ -1089,7 +1128,8 @@ def streams_update_norm(
     ``x_t = sum_s mix[s, t] x_s + scale * out_weights[t] * delta`` (``mix`` float32 ``[S, S]``, ``None`` = identity;
     ``out_weights`` float32 ``[S]``, ``None`` = ones), in place.  Then, with a ``norm_weight``, the combination
     ``u = sum_s read_weights[s] x_s`` (``None`` = the plain sum) goes through the norm (``layernorm``: mean subtracted,
-    variance the mean of squared deviations, no bias; ``rmsnorm``) and comes back ``[T, width]`` in ``out_dtype``.
+    variance the mean of squared deviations, no bias; ``rmsnorm``; ``dynamic_tanh``: ``tanh(norm_alpha * u) * norm_weight + norm_bias``
+    with ``norm_alpha`` float32 ``[1]`` and ``norm_bias`` float32 ``[width]``, no statistics and no eps) and comes back ``[T, width]`` in ``out_dtype``.
     With ``rows`` (int32) only those tokens are normalised, from updated values computed on the fly; the streams stay
     as they are."""
     _need_cuda(streams, delta, mix, out_weights, read_weights, norm_weight, rows)
@@ -1106,6 +1146,11 @@ def streams_update_norm(
         if tensor is not None:
             _need(tensor.dtype == torch.float32 and tuple(tensor.shape) == shape and tensor.is_contiguous(), f"streams_update_norm: {name} must be contiguous float32 {shape}")
     _need(kind in NORM_KINDS, f"streams_update_norm: unknown norm kind {kind!r}")
+    if kind == "dynamic_tanh" and norm_weight is not None:
+        _need_cuda(norm_bias, norm_alpha)
+        _need(norm_bias is not None and norm_bias.dtype == torch.float32 and norm_bias.shape == (width,) and norm_bias.is_contiguous()
+              and norm_alpha is not None and norm_alpha.dtype == torch.float32 and norm_alpha.numel() == 1,
+              "streams_update_norm: a dynamic tanh needs a float32 bias [width] and one float32 alpha")
     n_rows = tokens
     if rows is not None:
         _need(rows.dtype == torch.int32 and rows.dim() == 1 and rows.is_contiguous(), "streams_update_norm: rows must be contiguous int32")
@@ -1120,7 +1165,8 @@ def streams_update_norm(
     library = _library("streams.cu")
     _check(library, library.pylon_streams_update_norm(
         _ptr(streams), _ptr(delta), parts, delta_code, float(scale), _ptr(mix), _ptr(out_weights), _ptr(read_weights), _ptr(norm_weight),
-        _ptr(rows), _ptr(out), _dtype_code(out_dtype) if out is not None else F32, n_rows, tokens, count, width, float(eps), NORM_KINDS[kind], _stream()))
+        _ptr(rows), _ptr(out), _dtype_code(out_dtype) if out is not None else F32, n_rows, tokens, count, width, float(eps), NORM_KINDS[kind],
+        _ptr(norm_bias), _ptr(norm_alpha), _stream()))
     return out
 
 
@@ -1252,9 +1298,93 @@ def state_space(
 
 
 # ---------------------------------------------------------------------------------------
+# gated linear recurrence over channels; matrix memory
+# ---------------------------------------------------------------------------------------
+def _rows_meta(what: str, tokens: int, num_rows: int, **tensors: torch.Tensor) -> None:
+    sizes = {"token_row": tokens, "q_start": num_rows + 1, "slots": num_rows}
+    for name, tensor in tensors.items():
+        _need(tensor.dtype == torch.int32 and tensor.is_contiguous() and tensor.shape[0] >= sizes[name], f"{what}: {name} must be int32 [{sizes[name]}]")
+
+
+def linear_recurrence(proj: torch.Tensor, bias: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torch.Tensor, w_gates: torch.Tensor,
+                      gate_bias: torch.Tensor, lam: torch.Tensor, factor: float, state: torch.Tensor, token_row: torch.Tensor, q_start: torch.Tensor,
+                      slots: torch.Tensor, num_rows: int) -> torch.Tensor:
+    """A gated linear recurrence per channel over the tokens of a step (``csrc/linear_recurrence.cu`` has the equations).
+
+    ``proj [T, 2 C]``: the projection of the layer's input, columns ``[y | x]``, and ``bias`` float32 ``[2 C]`` to match; ``conv_weight``
+    float32 ``[C, taps]`` (the last tap weighs the current token) and ``conv_bias`` float32 ``[C]``; ``w_gates [blocks, 2 C / blocks, C / blocks]``
+    in ``proj``'s dtype: per block of channels the rows of the recurrence gate's map, then those of the input gate's; ``gate_bias`` float32
+    ``[2, C]`` (recurrence gate, input gate); ``lam`` float32 ``[C]``; ``state`` float32 ``[slots, C + (taps - 1) * C]``: per request the
+    recurrence's state and the convolution's last inputs, read at ``state[slots[row]]`` and advanced in place by the row's tokens.  Returns
+    ``[T, C]`` in ``proj``'s dtype: state times ``gelu_tanh(y)``, ready for the output projection."""
+    _need_cuda(proj, bias, conv_weight, conv_bias, w_gates, gate_bias, lam, state, token_row, q_start, slots)
+    tokens, channels = proj.shape[0], proj.shape[1] // 2
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == 2 * channels, "linear_recurrence: proj must be [T, 2 C]")
+    blocks = w_gates.shape[0]
+    _need(channels % blocks == 0 and w_gates.shape == (blocks, 2 * channels // blocks, channels // blocks) and w_gates.is_contiguous() and w_gates.dtype == proj.dtype,
+          "linear_recurrence: w_gates must be [blocks, 2 C / blocks, C / blocks] in proj's dtype")
+    _need(conv_weight.dtype == torch.float32 and conv_weight.dim() == 2 and conv_weight.shape[0] == channels and conv_weight.is_contiguous(),
+          "linear_recurrence: conv_weight must be contiguous float32 [C, taps]")
+    taps = conv_weight.shape[1]
+    for name, tensor, shape in (("bias", bias, (2 * channels,)), ("conv_bias", conv_bias, (channels,)), ("gate_bias", gate_bias, (2, channels)), ("lam", lam, (channels,))):
+        _need(tensor.dtype == torch.float32 and tuple(tensor.shape) == shape and tensor.is_contiguous(), f"linear_recurrence: {name} must be float32 {shape}")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] == channels * taps, "linear_recurrence: state must be contiguous float32 [slots, C * taps]")
+    _rows_meta("linear_recurrence", tokens, num_rows, token_row=token_row, q_start=q_start, slots=slots)
+    device, code = proj.device, _dtype_code(proj.dtype)
+    u32 = torch.empty((tokens, channels), dtype=torch.float32, device=device)
+    u16 = torch.empty((tokens, channels), dtype=proj.dtype, device=device) if proj.dtype != torch.float32 else None
+    library = _library("linear_recurrence.cu")
+    _check(library, library.pylon_linear_recurrence_conv(
+        _ptr(proj), proj.stride(0), channels, _ptr(bias[channels:]), _ptr(conv_weight), _ptr(conv_bias), taps, _ptr(state), state.shape[1], _ptr(token_row),
+        _ptr(q_start), _ptr(slots), _ptr(u32), _ptr(u16), channels, tokens, code, _stream()))
+    operand = (u32 if u16 is None else u16).view(tokens, blocks, channels // blocks)
+    gates = linear_heads(operand, w_gates, out_dtype=torch.float32)   # [T, blocks, 2 C / blocks], float32 sums whatever the operands
+    out = torch.empty((tokens, channels), dtype=proj.dtype, device=device)
+    _check(library, library.pylon_linear_recurrence_scan(
+        _ptr(proj), proj.stride(0), 0, channels, _ptr(bias), _ptr(bias[channels:]), _ptr(u32), _ptr(gates), _ptr(gate_bias), _ptr(gate_bias[1]), _ptr(lam),
+        float(factor), taps, _ptr(state), state.shape[1], _ptr(q_start), _ptr(slots), _ptr(out), channels, blocks, num_rows, code, _stream()))
+    return out
+
+
+def matrix_memory(proj: torch.Tensor, gate_logits: torch.Tensor, gate_bias: torch.Tensor, norm_weight: torch.Tensor, state: torch.Tensor,
+                  q_start: torch.Tensor, slots: torch.Tensor, heads: int, dim: int, vdim: int, cap: float, norm_eps: float, read_eps: float,
+                  num_rows: int) -> torch.Tensor:
+    """A matrix of memory per head with exponential gates over the tokens of a step (``csrc/matrix_memory.cu`` has the equations).
+
+    ``proj [T, 2 heads dim + 2 heads vdim]``: the projection of the layer's input, columns ``[q | k | v | g]``; ``gate_logits`` float32
+    ``[T, 2 heads]``: the input gates', then the forget gates'; ``gate_bias`` float32 ``[2, heads]`` to match; ``norm_weight`` float32
+    ``[heads * vdim]``; ``state`` float32 ``[slots, heads * (dim * vdim + dim + 1)]``: per request and head the matrix, the normaliser
+    and the running maximum, read at ``state[slots[row]]`` and advanced in place by the row's tokens.  Returns ``[T, heads * vdim]`` in
+    ``proj``'s dtype: the read-out, normed per head, times the weight and ``sigmoid(g)``, ready for the output projection."""
+    _need_cuda(proj, gate_logits, gate_bias, norm_weight, state, q_start, slots)
+    tokens = proj.shape[0]
+    columns = 2 * heads * (dim + vdim)
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and proj.shape[1] == columns, f"matrix_memory: proj must be [T, {columns}]")
+    _need(gate_logits.dtype == torch.float32 and gate_logits.shape == (tokens, 2 * heads) and gate_logits.is_contiguous(), "matrix_memory: gate_logits must be float32 [T, 2 heads]")
+    _need(gate_bias.dtype == torch.float32 and gate_bias.shape == (2, heads) and gate_bias.is_contiguous(), "matrix_memory: gate_bias must be float32 [2, heads]")
+    _need(norm_weight.dtype == torch.float32 and norm_weight.shape == (heads * vdim,) and norm_weight.is_contiguous(), "matrix_memory: norm_weight must be float32 [heads * vdim]")
+    _need(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] == heads * (dim * vdim + dim + 1),
+          "matrix_memory: state must be contiguous float32 [slots, heads * (dim * vdim + dim + 1)]")
+    _need(dim <= 256, f"matrix_memory: heads of {dim} query/key elements (at most 256)")
+    _rows_meta("matrix_memory", tokens, num_rows, q_start=q_start, slots=slots)
+    device, code = proj.device, _dtype_code(proj.dtype)
+    read = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=device)
+    fresh = torch.empty((num_rows, heads, dim + 1), dtype=torch.float32, device=device)
+    library = _library("matrix_memory.cu")
+    _check(library, library.pylon_matrix_memory_scan(
+        _ptr(proj), proj.stride(0), _ptr(gate_logits), _ptr(gate_bias), _ptr(gate_bias[1]), float(cap), float(read_eps), _ptr(state), state.shape[1],
+        _ptr(q_start), _ptr(slots), _ptr(read), _ptr(fresh), heads, dim, vdim, num_rows, code, _stream()))
+    launches[0] += 1   # the walk is followed by the small kernel that puts the normaliser and the maximum into the slots
+    out = torch.empty((tokens, heads * vdim), dtype=proj.dtype, device=device)
+    _check(library, library.pylon_matrix_memory_out(_ptr(read), _ptr(proj), proj.stride(0), 2 * heads * dim + heads * vdim, _ptr(norm_weight), float(norm_eps),
+                                                    _ptr(out), heads, vdim, tokens, code, _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------------------
 # small kernels between products
 # ---------------------------------------------------------------------------------------
-ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "gelu": 3}   # "gelu": the exact form, with erf
 
 
 def concat_cast(a: torch.Tensor, b: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
@@ -1317,6 +1447,37 @@ def mean_of_normed(outputs: Sequence[torch.Tensor], weights: Sequence[torch.Tens
     return out
 
 
+def weighted_sum(outputs: Sequence[torch.Tensor], scales: Sequence[float], dtype: torch.dtype) -> torch.Tensor:
+    """``sum_i scales[i] * y_i`` in float32.  Each ``y_i`` is ``[T, width]`` in ``dtype`` or float32 partial sums ``[parts, T, width]``
+    whose sum is the output.  Returns float32 ``[1, T, width]``: in the form of partial sums, so that the residual stream takes it
+    in 32-bit."""
+    _need(1 <= len(outputs) == len(scales) <= 4, "weighted_sum: one to four outputs, a factor for each")
+    _need_cuda(*outputs)
+    tokens, width = outputs[0].shape[-2:]
+    parts, floats = [], []
+    for y in outputs:
+        _need(y.is_contiguous() and y.shape[-2:] == (tokens, width) and ((y.dim() == 3 and y.dtype == torch.float32) or (y.dim() == 2 and y.dtype == dtype)),
+              "weighted_sum: an output is [T, width] in the compute dtype or float32 [parts, T, width]")
+        parts.append(y.shape[0] if y.dim() == 3 else 1)
+        floats.append(1 if y.dim() == 3 or y.dtype == torch.float32 else 0)
+    count = len(outputs)
+    out = torch.empty((1, tokens, width), dtype=torch.float32, device=outputs[0].device)
+    library = _library("combine.cu")
+    _check(library, library.pylon_weighted_sum(
+        (c_void_p * count)(*[y.data_ptr() for y in outputs]), (c_int * count)(*parts), (c_int * count)(*floats),
+        (c_float * count)(*[float(scale) for scale in scales]), count, _ptr(out), tokens * width, _dtype_code(dtype), _stream()))
+    return out
+
+
+def activation_in_place(x: torch.Tensor, kind: str) -> torch.Tensor:
+    """In place: ``x <- act(x)`` element by element on a contiguous tensor."""
+    _need_cuda(x)
+    _need(kind in ACTIVATIONS and x.is_contiguous(), f"activation: {kind!r} on a contiguous tensor")
+    library = _library("combine.cu")
+    _check(library, library.pylon_activation(_ptr(x), x.numel(), ACTIVATIONS[kind], _dtype_code(x.dtype), _stream()))
+    return x
+
+
 # ---------------------------------------------------------------------------------------
 # mixture of experts
 # ---------------------------------------------------------------------------------------
@@ -1324,7 +1485,9 @@ EXPERT_TILE_ROWS = 128   # the row tile of the grouped tcgen05 product
 
 
 def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[torch.Tensor], w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                   top: int, activation: str = "silu", interleaved: bool = False) -> torch.Tensor:
+                   top: int, activation: str = "silu", interleaved: bool = False, gated: bool = True, routing: str = "softmax",
+                   correction: Optional[torch.Tensor] = None, groups: int = 0, groups_keep: int = 0, share_eps: float = 0.0,
+                   common_up: Optional[torch.Tensor] = None, common_down: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``sum over a token's top experts e of share_e * W_down,e (act(W_gate,e h) * (W_up,e h))`` (``csrc/experts.cu``).
 
     ``h [T, width]``; ``router`` float32 ``[experts, width]`` and ``router_bias`` float32 ``[experts]`` (or None): the logits are
@@ -1332,24 +1495,39 @@ def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[
     every expert's rows stacked by :func:`interleave_gate_up`) and ``w_down [experts, width, F]`` in ``h``'s dtype.  Returns float32
     ``[1, T, width]`` (the form of partial sums: the residual stream takes it in 32-bit).
 
+    ``gated=False``: an expert is ``W_down act(W_up h)`` and ``w_gate_up`` holds the up rows only, ``[experts, F, width]``.
+    ``routing="sigmoid"``: the scores are ``sigmoid(z)``; the choice goes by score plus ``correction`` (float32 ``[experts]`` or None), with
+    ``groups`` > 0 only among the experts of the ``groups_keep`` groups of neighbours whose two largest choice scores add up to most; the
+    shares are the chosen experts' scores divided by their sum plus ``share_eps``.  ``common_up [G, width]`` / ``common_down [width, G]``:
+    an ungated expert that every token goes through, added times ``sigmoid(w h)`` with ``w`` the row that ``router`` then holds behind
+    the experts' rows (``[experts + 1, width]``).
+
     The tokens are sorted by expert on the device.  A step of few tokens runs the experts' products from row tiles of 32 slots that
     gather their rows themselves (``mma.sync``, bound by the matrices coming from memory); a bfloat16 step with about half a
-    128-row tile or more per expert, interleaved weights and ``silu`` copies the rows into their sorted order and runs both
-    products on the grouped form of the tcgen05 kernel (the gated unit in the first one's epilogue)."""
-    _need_cuda(h, router, router_bias, w_gate_up, w_down)
+    128-row tile or more per expert (gated: interleaved weights and ``silu``) copies the rows into their sorted order and runs both
+    products on the grouped form of the tcgen05 kernel (the gated unit in the first one's epilogue; an ungated expert's activation
+    is a pass of its own between the two)."""
+    _need_cuda(h, router, router_bias, w_gate_up, w_down, correction, common_up, common_down)
     _need(activation in ACTIVATIONS, f"expert_mixture: activation {activation!r}")
+    _need(routing in ("softmax", "sigmoid"), f"expert_mixture: routing {routing!r}")
     _need(h.dim() == 2 and h.stride(1) == 1, "expert_mixture: h must be [T, width]")
     tokens, width = h.shape
-    experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // 2
-    _need(w_gate_up.shape == (experts, 2 * inner, width) and w_down.shape == (experts, width, inner) and w_gate_up.is_contiguous() and w_down.is_contiguous()
-          and w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype, "expert_mixture: w_gate_up [experts, 2 F, width] and w_down [experts, width, F] in h's dtype")
-    _need(router.dtype == torch.float32 and router.shape == (experts, width) and router.is_contiguous(), "expert_mixture: router must be float32 [experts, width]")
+    halves = 2 if gated else 1
+    experts, inner = w_gate_up.shape[0], w_gate_up.shape[1] // halves
+    _need(w_gate_up.shape == (experts, halves * inner, width) and w_down.shape == (experts, width, inner) and w_gate_up.is_contiguous() and w_down.is_contiguous()
+          and w_gate_up.dtype == h.dtype and w_down.dtype == h.dtype, "expert_mixture: w_gate_up [experts, 2 F, width] (ungated: [experts, F, width]) and w_down [experts, width, F] in h's dtype")
+    scored = routing == "sigmoid"
+    extra = 1 if common_up is not None else 0
+    _need(scored or (correction is None and not groups and not extra), "expert_mixture: a correction, groups and a common expert go with sigmoid routing")
+    _need(router.dtype == torch.float32 and router.shape == (experts + extra, width) and router.is_contiguous(), "expert_mixture: router must be float32 [experts (+ 1), width]")
     _need(router_bias is None or (router_bias.dtype == torch.float32 and router_bias.shape == (experts,)), "expert_mixture: router_bias must be float32 [experts]")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.shape == (experts,) and correction.is_contiguous()), "expert_mixture: correction must be float32 [experts]")
     _need(1 <= top <= experts, f"expert_mixture: top {top} of {experts} experts")
-    _need(not interleaved or inner % 8 == 0, "expert_mixture: interleaved rows need an inner width that is a multiple of 8")
+    _need(not interleaved or (gated and inner % 8 == 0), "expert_mixture: interleaved rows need a gated unit of an inner width that is a multiple of 8")
+    _need((common_up is None) == (common_down is None), "expert_mixture: a common expert has both its matrices")
     library = _library("experts.cu")
     pairs = tokens * top
-    grouped = (interleaved and h.dtype == torch.bfloat16 and activation == "silu" and pairs * 2 >= EXPERT_TILE_ROWS * experts and width % 8 == 0
+    grouped = ((not gated or (interleaved and activation == "silu")) and h.dtype == torch.bfloat16 and pairs * 2 >= EXPERT_TILE_ROWS * experts and width % 8 == 0
                and inner % 8 == 0 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0)
     tile = EXPERT_TILE_ROWS if grouped else library.pylon_experts_row_tile()
     max_tiles = min(pairs, experts) + pairs // tile    # every expert with tokens ends in at most one partly filled tile
@@ -1360,10 +1538,16 @@ def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[
     slot_of = torch.empty((pairs,), dtype=torch.int32, device=device)
     source = torch.empty((max_slots,), dtype=torch.int32, device=device)
     tile_expert = torch.empty((max_tiles,), dtype=torch.int32, device=device)
+    common_gate = torch.empty((tokens,), dtype=torch.float32, device=device) if extra else None
     code, kind = _dtype_code(h.dtype), ACTIVATIONS[activation]
     _check(library, library.pylon_experts_route(_ptr(h), h.stride(0), _ptr(router), _ptr(router_bias), _ptr(chosen), _ptr(share), width, experts, top,
-                                                tokens, code, _stream()))
+                                                tokens, code, int(scored), _ptr(correction), int(groups or 0), int(groups_keep or 0), float(share_eps), extra,
+                                                _ptr(common_gate), _stream()))
     _check(library, library.pylon_experts_plan(_ptr(chosen), _ptr(slot_of), _ptr(source), _ptr(tile_expert), pairs, experts, max_slots, max_tiles, tile, _stream()))
+    common, common_code = None, F32
+    if extra:   # the expert of every token: two plain products around the activation
+        common = linear(activation_in_place(linear(h, common_up), activation), common_down)
+        common_code = _dtype_code(common.dtype)
     out = torch.empty((1, tokens, width), dtype=torch.float32, device=device)
     if grouped:
         product = _library("gemm_tcgen05.cu")
@@ -1371,28 +1555,33 @@ def expert_mixture(h: torch.Tensor, router: torch.Tensor, router_bias: Optional[
         rows = torch.empty((max_slots, width), dtype=h.dtype, device=device)
         _check(library, library.pylon_experts_sort_rows(_ptr(h), h.stride(0), _ptr(source), _ptr(rows), width, top, max_slots, code, _stream()))
         act = torch.empty((max_slots, inner), dtype=h.dtype, device=device)
-        _check(product, product.pylon_gemm_tcgen05_grouped(_ptr(rows), _ptr(w_gate_up), _ptr(act), max_slots, 2 * inner, width, width, width, inner, 1,
-                                                           _ptr(tile_expert), experts, error, sms, _stream()))
+        _check(product, product.pylon_gemm_tcgen05_grouped(_ptr(rows), _ptr(w_gate_up), _ptr(act), max_slots, halves * inner, width, width, width, inner,
+                                                           1 if gated else 0, _ptr(tile_expert), experts, error, sms, _stream()))
+        if not gated:
+            activation_in_place(act, activation)   # (rows of empty slots hold act(0) of zeros: they are never gathered)
         y = torch.empty((max_slots, width), dtype=h.dtype, device=device)
         _check(product, product.pylon_gemm_tcgen05_grouped(_ptr(act), _ptr(w_down), _ptr(y), max_slots, width, inner, inner, inner, width, 0,
                                                            _ptr(tile_expert), experts, error, sms, _stream()))
-        _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, code, _stream()))
+        _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, code, _ptr(common), _ptr(common_gate),
+                                                     common_code, _stream()))
         return out
     act = torch.empty((max_slots, inner), dtype=h.dtype, device=device)
     _check(library, library.pylon_experts_product(_ptr(h), h.stride(0), _ptr(w_gate_up), _ptr(source), _ptr(tile_expert), 1, top, _ptr(act), inner, width,
-                                                  max_tiles, 1, kind, int(interleaved), code, _stream()))
+                                                  max_tiles, 1 if gated else 2, kind, int(interleaved), code, _stream()))
     y = torch.empty((max_slots, width), dtype=torch.float32, device=device)
     _check(library, library.pylon_experts_product(_ptr(act), inner, _ptr(w_down), _ptr(source), _ptr(tile_expert), 0, 1, _ptr(y), width, inner,
                                                   max_tiles, 0, kind, 0, code, _stream()))
-    _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, _dtype_code(torch.float32), _stream()))
+    _check(library, library.pylon_experts_gather(_ptr(y), _ptr(slot_of), _ptr(share), _ptr(out), tokens, width, top, _dtype_code(torch.float32), _ptr(common),
+                                                 _ptr(common_gate), common_code, _stream()))
     return out
 
 
 # ---------------------------------------------------------------------------------------
 # products per head
 # ---------------------------------------------------------------------------------------
-def linear_heads(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear_heads(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """One product per head: ``y[t, h] = w[h] @ x[t, h]`` for ``x [T, H, K]``, ``w [H, N, K]`` -> ``[T, H, N]``.
+    ``out_dtype=torch.float32`` keeps the 32-bit sums of a bfloat16 product (logits of gates, say).
 
     ``x`` and ``out`` may be views whose heads are slices of wider rows (any token and head strides; the last dimension
     contiguous).  float32 runs the plain-FMA kernel, one grid layer per head; bfloat16 goes to the library's batched
@@ -1402,6 +1591,11 @@ def linear_heads(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
     _need(x.dtype == w.dtype and x.stride(2) == 1 and w.is_contiguous(), "linear_heads: one dtype, the reduced dimension contiguous, the weights contiguous")
     tokens, heads, k = x.shape
     n = w.shape[1]
+    if out_dtype is not None and out_dtype != x.dtype:
+        _need(out is None and x.dtype == torch.bfloat16 and out_dtype == torch.float32, "linear_heads: only a bfloat16 product can keep its float32 sums")
+        if tokens == 0:
+            return torch.empty((tokens, heads, n), dtype=torch.float32, device=x.device)
+        return torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32).transpose(0, 1).contiguous()
     if out is None:
         out = torch.empty((tokens, heads, n), dtype=x.dtype, device=x.device)
     _need(out.shape == (tokens, heads, n) and out.dtype == x.dtype and out.stride(2) == 1, "linear_heads: out must be [T, H, N] with its last dimension contiguous")

@@ -1,5 +1,5 @@
 """Parts a layer is put together from.  Importing the package registers the built-in kinds."""
-from pylon_b200.parts import attention, block, delta, latent, lightning, mlp, norm, parallel, rope, state_space  # noqa: F401  (registration)
+from pylon_b200.parts import attention, block, delta, latent, lightning, memory, mlp, norm, parallel, recurrence, rope, state_space  # noqa: F401  (registration)
 from pylon_b200.parts.base import (  # noqa: F401
     BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, CacheNeed, FeedForward, KVNeed, LayerCache,
     Mixer, Norm, Part, PositionEncoding, ResidualStream, StateNeed, StepView, StreamRoute, TensorDecl,

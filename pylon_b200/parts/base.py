@@ -62,7 +62,8 @@ class KVNeed:
     ``window``: a query at position p reads keys at positions (p - window, p]; ``None``
     reads all of them.  ``chunk``: a query at position p reads only keys of its own chunk of
     positions, ``[p - p % chunk, p]``.  Either lets the manager give pages back that no later
-    token can read.  Layers whose KVNeed is equal share a page pool (a cache group).
+    token can read.  ``keep_first``: the keys at positions below it stay readable whatever the window says,
+    so the pages that hold them are never given back early.  Layers whose KVNeed is equal share a page pool (a cache group).
     """
 
     n_kv_heads: int
@@ -70,6 +71,7 @@ class KVNeed:
     window: Optional[int] = None
     value_dim: Optional[int] = None
     chunk: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def bounded(self) -> bool:

@@ -139,3 +139,41 @@ class HyperPreNormBlock(Block):
         stream.add(self.mixer.forward(self.mixer_norm.apply(stream, read=self.read[1]), step, cache), self.residual_mult, self.route[1])
         if self.feed_forward is not None:
             stream.add(self.feed_forward.forward(self.ffn_norm.apply(stream, read=self.read[2]), step), self.residual_mult, self.route[2])
+
+
+@BLOCKS.register("parallel_sublayers")
+class ParallelSublayers(Block):
+    """One norm, two readers: with ``h = norm(x)`` the layer is ``x = x + (mixer(h) + feed_forward(h))``.  Both outputs join the
+    32-bit residual sum (the mixer's first, the feed-forward's at the next norm); ``feed_forward=None`` leaves the second out.
+    The tensors: the mixer's under ``mixer_prefix``, the feed-forward's under ``ffn_prefix``, the norm's under ``norm_prefix``."""
+
+    def __init__(self, mixer: PartSpec, feed_forward: Optional[PartSpec], norm: PartSpec, mixer_prefix: str = "mix.", ffn_prefix: str = "mlp.",
+                 norm_prefix: str = "norm1") -> None:
+        self.mixer = MIXERS.build(mixer)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward is not None else None
+        self.norm = NORMS.build(norm)
+        self._children = [(mixer_prefix, self.mixer), (norm_prefix, self.norm)]
+        if self.feed_forward is not None:
+            self._children.append((ffn_prefix, self.feed_forward))
+
+    @property
+    def takes_padding(self) -> bool:
+        return bool(self.mixer.takes_padding and (self.feed_forward is None or self.feed_forward.takes_padding))
+
+    def tensors(self) -> Sequence[TensorDecl]:
+        return [decl for prefix, part in self._children for decl in _prefixed(prefix, part.tensors())]
+
+    def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        for prefix, part in self._children:
+            # the norm's own tensor is the bare prefix: it must not take the mixer's or the feed-forward's for its own
+            mine = {name: tensor for name, tensor in _strip(prefix, tensors).items() if name in {decl.name for decl in part.tensors()}}
+            part.load(mine, dtype, device)
+
+    def weight_bytes(self) -> int:
+        return sum(part.weight_bytes() for _, part in self._children)
+
+    def forward(self, stream: ResidualStream, step: StepView, cache: LayerCache) -> None:
+        h = self.norm.apply(stream)
+        stream.add(self.mixer.forward(h, step, cache))
+        if self.feed_forward is not None:
+            stream.add(self.feed_forward.forward(h, step))

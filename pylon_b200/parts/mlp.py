@@ -123,18 +123,38 @@ class ExpertMixture(FeedForward):
     goes through the ``top`` whose router logits ``W_r x (+ b_r)`` are largest, weighted by the softmax over just those logits.
     The router's weights stay float32 and its logits are float32 sums whatever the compute dtype.  An expert's tensors are
     ``e<i>.gate`` / ``.up`` / ``.down``; they are stacked at load, and the tokens of a step are sorted by expert on the device
-    (``csrc/experts.cu``), so a step is the same sequence of launches whatever the routing."""
+    (``csrc/experts.cu``), so a step is the same sequence of launches whatever the routing.
+
+    Other forms.  ``gated=False``: an expert is ``down_e(act(up_e(x)))`` and has no gate tensor.  ``routing="sigmoid"``: the scores
+    are ``sigmoid(W_r x)``; the ``top`` experts are chosen by score plus a learnt correction (``correction=True``: tensor
+    ``correction [experts]``), with ``groups`` only among the experts of the ``groups_keep`` groups of neighbours whose two largest
+    choice scores add up to most; the weights are the chosen experts' scores, without the correction, divided by their sum plus
+    ``share_eps``.  ``shared_intermediate`` F: one more ungated expert ``shared.up [F, width]`` / ``shared.down`` that every token goes
+    through, added times ``sigmoid(w x)``, ``w`` the tensor ``shared.sg [1, width]`` (it rides in the router's product)."""
 
     def __init__(self, width: int, intermediate: int, experts: int, top: int, activation: str = "silu", router_bias: bool = False,
-                 names: Optional[Mapping[str, str]] = None) -> None:
+                 names: Optional[Mapping[str, str]] = None, gated: bool = True, routing: str = "softmax", correction: bool = False,
+                 groups: Optional[int] = None, groups_keep: Optional[int] = None, share_eps: float = 0.0,
+                 shared_intermediate: Optional[int] = None) -> None:
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"unknown activation {activation!r} (known: {', '.join(ops.ACTIVATIONS)})")
         self.width, self.intermediate, self.experts, self.top = int(width), int(intermediate), int(experts), int(top)
         if not 1 <= self.top <= self.experts:
             raise ValueError(f"a token cannot use {top} of {experts} experts")
-        self.activation, self.router_bias = activation, bool(router_bias)
-        self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}.", "gate": "gate", "up": "up", "down": "down", **(names or {})}
-        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+        if routing not in ("softmax", "sigmoid"):
+            raise ValueError(f"routing is 'softmax' or 'sigmoid', not {routing!r}")
+        self.activation, self.router_bias, self.gated, self.routing = activation, bool(router_bias), bool(gated), routing
+        self.correction_used = bool(correction)
+        self.groups, self.groups_keep = (0, 0) if groups is None else (int(groups), int(groups_keep or groups))
+        self.share_eps = float(share_eps)
+        self.shared_intermediate = None if shared_intermediate is None else int(shared_intermediate)
+        if routing != "sigmoid" and (self.correction_used or self.groups or self.shared_intermediate is not None):
+            raise ValueError("a correction, groups of experts and a shared expert go with sigmoid routing")
+        if self.groups and (self.experts % self.groups or not 1 <= self.groups_keep <= self.groups or self.top > self.groups_keep * (self.experts // self.groups)):
+            raise ValueError(f"{experts} experts in {groups} groups of which {groups_keep} are kept, {top} experts a token")
+        self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}.", "gate": "gate", "up": "up", "down": "down",
+                      "correction": "correction", "shared_up": "shared.up", "shared_down": "shared.down", "shared_gate": "shared.sg", **(names or {})}
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = self.correction = self.w_shared_up = self.w_shared_down = None
         self.interleaved = False
 
     def _expert(self, index: int, key: str) -> str:
@@ -143,26 +163,42 @@ class ExpertMixture(FeedForward):
     def tensors(self) -> Sequence[TensorDecl]:
         decls = []
         for e in range(self.experts):
-            decls += [TensorDecl(self._expert(e, "gate"), (self.intermediate, self.width)), TensorDecl(self._expert(e, "up"), (self.intermediate, self.width)),
-                      TensorDecl(self._expert(e, "down"), (self.width, self.intermediate))]
+            if self.gated:
+                decls.append(TensorDecl(self._expert(e, "gate"), (self.intermediate, self.width)))
+            decls += [TensorDecl(self._expert(e, "up"), (self.intermediate, self.width)), TensorDecl(self._expert(e, "down"), (self.width, self.intermediate))]
         decls.append(TensorDecl(self.names["router"], (self.experts, self.width), "vector", (0.0, 0.5)))
         if self.router_bias:
             decls.append(TensorDecl(self.names["router_bias"], (self.experts,), "vector", (0.0, 0.1)))
+        if self.correction_used:
+            decls.append(TensorDecl(self.names["correction"], (self.experts,), "vector", (0.0, 0.1)))
+        if self.shared_intermediate is not None:
+            decls += [TensorDecl(self.names["shared_up"], (self.shared_intermediate, self.width)), TensorDecl(self.names["shared_down"], (self.width, self.shared_intermediate)),
+                      TensorDecl(self.names["shared_gate"], (1, self.width), "vector", (0.0, 0.5))]
         return decls
 
     def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
         # In bfloat16 with silu an expert's gate and up rows alternate in groups of 8, the layout the tcgen05 product's gated epilogue
         # takes (the products for few tokens read either layout); otherwise the two halves lie one after the other.
-        self.interleaved = dtype == torch.bfloat16 and self.activation == "silu" and self.intermediate % 8 == 0
-        pair = ops.interleave_gate_up if self.interleaved else (lambda gate, up: torch.cat((gate, up), dim=0))
-        self.w_gate_up = torch.stack([pair(tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]) for e in range(self.experts)]).contiguous()
+        self.interleaved = self.gated and dtype == torch.bfloat16 and self.activation == "silu" and self.intermediate % 8 == 0
+        if self.gated:
+            pair = ops.interleave_gate_up if self.interleaved else (lambda gate, up: torch.cat((gate, up), dim=0))
+            self.w_gate_up = torch.stack([pair(tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]) for e in range(self.experts)]).contiguous()
+        else:
+            self.w_gate_up = torch.stack([tensors[self._expert(e, "up")] for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(self.experts)]).contiguous()
         self.w_router = tensors[self.names["router"]].contiguous()
         self.b_router = tensors[self.names["router_bias"]].contiguous() if self.router_bias else None
+        self.correction = tensors[self.names["correction"]].contiguous() if self.correction_used else None
+        if self.shared_intermediate is not None:
+            self.w_router = torch.cat((self.w_router, tensors[self.names["shared_gate"]]), dim=0).contiguous()   # the gate's row behind the experts' rows
+            self.w_shared_up, self.w_shared_down = tensors[self.names["shared_up"]].contiguous(), tensors[self.names["shared_down"]].contiguous()
 
     def weight_bytes(self) -> int:
         """What a step of many tokens reads: every expert (a step of few tokens reads ``top`` experts a token at most)."""
-        return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size() + self.w_router.numel() * 4
+        shared = 0 if self.w_shared_up is None else self.w_shared_up.numel() + self.w_shared_down.numel()
+        return (self.w_gate_up.numel() + self.w_down.numel() + shared) * self.w_down.element_size() + self.w_router.numel() * 4
 
     def forward(self, h: torch.Tensor, step: StepView) -> torch.Tensor:
-        return ops.expert_mixture(h, self.w_router, self.b_router, self.w_gate_up, self.w_down, self.top, self.activation, self.interleaved)
+        return ops.expert_mixture(h, self.w_router, self.b_router, self.w_gate_up, self.w_down, self.top, self.activation, self.interleaved,
+                                  gated=self.gated, routing=self.routing, correction=self.correction, groups=self.groups, groups_keep=self.groups_keep,
+                                  share_eps=self.share_eps, common_up=self.w_shared_up, common_down=self.w_shared_down)

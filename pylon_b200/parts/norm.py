@@ -84,3 +84,39 @@ class LayerNorm(Norm):
 
     def apply(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None) -> torch.Tensor:
         return _apply_to_streams(self, "layernorm", stream, rows, read)
+
+
+@NORMS.register("dynamic_tanh")
+class DynamicTanh(Norm):
+    """A norm without statistics: ``tanh(alpha * x) * weight + bias`` in float32, ``alpha`` one learnt number, ``weight`` and ``bias``
+    vectors of the width.  Nothing is summed over the row, so there is no eps.  Like the other norms it is where a pending delta
+    joins the residual stream.  The three tensors are the part's prefix plus ``weight_name``, ``alpha_name`` and ``bias_name``."""
+
+    def __init__(self, width: int, weight_name: str = "weight", alpha_name: str = "alpha", bias_name: str = "bias") -> None:
+        self.width = int(width)
+        self.weight_name, self.alpha_name, self.bias_name = weight_name, alpha_name, bias_name
+        self.eps = 0.0
+        self.weight = self.alpha = self.bias = None
+        self.dtype: Optional[torch.dtype] = None
+
+    def tensors(self) -> Sequence[TensorDecl]:
+        return (TensorDecl(self.weight_name, (self.width,), "vector"), TensorDecl(self.alpha_name, (), "vector", (0.5, 0.05)),
+                TensorDecl(self.bias_name, (self.width,), "vector", (0.0, 0.02)))
+
+    def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        self.weight, self.bias = tensors[self.weight_name].contiguous(), tensors[self.bias_name].contiguous()
+        self.alpha = tensors[self.alpha_name].reshape(1).contiguous()
+        self.dtype = dtype
+
+    def weight_bytes(self) -> int:
+        return self.width * 8 + 4
+
+    def apply(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, read: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if rows is None:
+            delta, scale, route = stream.take_pending()
+        else:   # the stream stays as it is: what is pending stays pending
+            delta, scale, route = stream.pending, stream.pending_scale, stream.pending_route
+        return ops.streams_update_norm(
+            stream.residual, delta, scale, None if route is None else route.mix, None if route is None else route.out, read,
+            self.weight, 0.0, "dynamic_tanh", self.dtype, rows=rows, norm_bias=self.bias, norm_alpha=self.alpha,
+        )

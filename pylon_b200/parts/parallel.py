@@ -58,3 +58,31 @@ class ParallelMixers(Mixer):
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
         outputs = [mixer.forward(h, step, cache) for mixer in self.mixers]   # each takes from the layer's cache what it asked for
         return ops.mean_of_normed(outputs, self.norm_weights, self.norm_eps, self.dtype)
+
+
+@MIXERS.register("weighted_mixers")
+class WeightedMixers(ParallelMixers):
+    """Mixers side by side whose outputs are added, each times a fixed factor: ``y = sum_i scale_i * mixer_i(h)``, one float32
+    kernel whose result enters the residual sum in 32-bit.  No norms, so no tensors beyond the mixers' own."""
+
+    def __init__(self, mixers: Sequence[PartSpec], prefixes: Sequence[str], scales: Sequence[float]) -> None:
+        if not 1 <= len(mixers) <= 4 or len(prefixes) != len(mixers) or len(scales) != len(mixers):
+            raise ValueError("one to four mixers side by side, each with a prefix for its tensors and a factor")
+        self.mixers = [MIXERS.build(spec) for spec in mixers]
+        self.prefixes, self.norm_names = tuple(prefixes), ()
+        self.scales = tuple(float(scale) for scale in scales)
+
+    def tensors(self) -> Sequence[TensorDecl]:
+        return [TensorDecl(prefix + d.name, d.shape, d.role, d.init) for prefix, mixer in zip(self.prefixes, self.mixers) for d in mixer.tensors()]
+
+    def load(self, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype, device: torch.device) -> None:
+        for prefix, mixer in zip(self.prefixes, self.mixers):
+            mixer.load({name[len(prefix):]: tensor for name, tensor in tensors.items() if name.startswith(prefix)}, dtype, device)
+        self.dtype = dtype
+
+    def weight_bytes(self) -> int:
+        return sum(mixer.weight_bytes() for mixer in self.mixers)
+
+    def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
+        outputs = [mixer.forward(h, step, cache) for mixer in self.mixers]
+        return ops.weighted_sum(outputs, self.scales, self.dtype)
