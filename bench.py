@@ -18,8 +18,8 @@ decode steps) at B = 1, 8, 64 with its share of the HBM roofline; the output rat
 serving workloads at the 8B and 14B shapes; and a full-depth float32 run at the 14B shape with
 its largest logit error against the plain implementation.
 
-``--workload designs`` is another measurement with a line of its own: Vopepel, Fikerax and Zemavik beside Qwen3 dense at equal width, depth,
-heads, feed-forward and vocabulary (sizes ``2k`` and ``4k``; ``--designs`` picks among the four): prefill of a 2,048-token prompt, decode at batch 8 and a context of 2,048,
+``--workload designs`` is another measurement with a line of its own: Vopepel, Fikerax, Zemavik and Rirusun beside Qwen3 dense at equal width, depth,
+heads, feed-forward and vocabulary (sizes ``2k`` and ``4k``; ``--designs`` picks among the five): prefill of a 2,048-token prompt, decode at batch 8 and a context of 2,048,
 and the time of every kernel entry point in one step of each kind.
 """
 from __future__ import annotations
@@ -475,7 +475,7 @@ def run_serving_workload(name: str, torch) -> dict:
 
 
 # ---------------------------------------------------------------------------------------
-# Vopepel, Fikerax and Zemavik beside Qwen3 at equal size (--workload designs)
+# Vopepel, Fikerax, Zemavik and Rirusun beside Qwen3 at equal size (--workload designs)
 # ---------------------------------------------------------------------------------------
 DESIGN_SIZES = {
     # width, layers, heads / kv heads / head size of the attention, inner width of the feed-forward, vocabulary
@@ -486,8 +486,8 @@ DESIGN_CONTEXT = 2_048
 _TIMED_OPS = ("linear", "linear_for_residual", "linear_swiglu", "linear_for_rotation", "linear_qkv_rotated", "paged_attention", "gated_delta_rule",
               "streams_update_norm", "add_rmsnorm", "swiglu", "qk_norm_mix_kv_write", "qk_norm_rope_kv_write", "embed_gather", "lightning_attention",
               "qkv_rotate_write", "latent_norm_rotate_write", "rotate_heads", "linear_heads", "state_space", "expert_mixture", "mean_of_normed",
-              "gated_unit", "add_bias", "concat_cast")
-DESIGNS = ("vopepel", "qwen3", "fikerax", "zemavik")
+              "gated_unit", "add_bias", "concat_cast", "linear_recurrence", "matrix_memory", "weighted_sum", "residual_add")
+DESIGNS = ("vopepel", "qwen3", "fikerax", "zemavik", "rirusun")
 
 
 def vopepel_fields(size: dict) -> dict:
@@ -543,6 +543,31 @@ def zemavik_fields(size: dict) -> dict:
             "right": {"heads": size["width"] // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}}}
     return {"architecture": "Zemavik", "vocab": size["vocab"], "width": size["width"], "max_positions": 4_096, "norm": {"eps": 1e-5},
             "loop": {"start": 0, "stop": size["layers"], "times": 1}, "layers": [layer(index) for index in range(size["layers"])]}
+
+
+def rirusun_fields(size: dict) -> dict:
+    """A Rirusun model of the given size: of every four layers the first and the last are attention (a window of 1,024 positions that
+    keeps the first 4, a bias table of 32 rows that ends at distance 1,024, a sink) beside a gated linear recurrence as wide as the model
+    (gates in blocks of 256 channels, a convolution of 4 taps), the second a matrix memory of 8 heads (keys a sixteenth, values an
+    eighth of the width each), the third latent attention (a cached row of 512 + 64 numbers per token, queries straight from the input);
+    every layer's feed-forward is a mixture of 8 ungated experts of half the inner width in 4 groups of which 2 are kept and a token
+    uses 2, and a shared expert of the same width; no layer runs twice, so that the depth is the other designs'."""
+    def layer(index: int) -> dict:
+        mlp = {"kind": "moe", "expert": {"ff": size["ff"] // 2}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}},
+               "shared": {"ff": size["ff"] // 2}}
+        heads, dim, width = size["heads"], size["head_dim"], size["width"]
+        if index % 4 == 1:
+            return {"type": "mlstm", "mlp": mlp, "mixer": {"heads": 8, "dim": width // 16, "vdim": width // 8, "gate_cap": 15.0}}
+        if index % 4 == 2:
+            return {"type": "latent_attention", "mlp": mlp, "mixer": {
+                "heads": heads, "dim": dim, "rot_dim": dim // 2, "vdim": dim, "kv_rank": 512, "scale": (dim + dim // 2) ** -0.5,
+                "rot": {"dims": dim // 2, "base": 10_000.0, "scaling": {"factor": 8.0, "original": 4_096, "fast": 32.0, "slow": 1.0}}}}
+        return {"type": "parallel", "mlp": mlp, "mixer": {
+            "left": {"heads": heads, "kv_heads": size["kv_heads"], "dim": dim, "vdim": dim, "scale": dim ** -0.5, "bias_max": 1_024, "bias_rows": 32,
+                     "mask": {"size": 1_024, "keep_first": 4}},
+            "left_scale": 1.0, "right": {"width": width, "blocks": width // 256, "conv": 4}, "right_scale": 1.0}}
+    return {"architecture": "Rirusun", "vocab": size["vocab"], "width": size["width"], "embedding": {"scale": size["width"] ** 0.5}, "norm": {"eps": 1e-5},
+            "layers": [layer(index) for index in range(size["layers"])]}
 
 
 def qwen3_fields(size: dict) -> dict:
@@ -668,13 +693,14 @@ def run_design_comparison(torch, sizes, batch: int, steps: int, designs=DESIGNS)
     import numpy as np
 
     from pylon_b200.config import EngineConfig, Qwen3Config
-    from pylon_b200.config.model_config import FikeraxConfig, VopepelConfig, ZemavikConfig
+    from pylon_b200.config.model_config import FikeraxConfig, RirusunConfig, VopepelConfig, ZemavikConfig
     from pylon_b200.engine import Engine
     from pylon_b200.kernels import ops
 
     peak = peaks()
     made = {"vopepel": lambda size: VopepelConfig.from_dict(vopepel_fields(size)), "qwen3": lambda size: Qwen3Config(**qwen3_fields(size)),
-            "fikerax": lambda size: FikeraxConfig.from_dict(fikerax_fields(size)), "zemavik": lambda size: ZemavikConfig.from_dict(zemavik_fields(size))}
+            "fikerax": lambda size: FikeraxConfig.from_dict(fikerax_fields(size)), "zemavik": lambda size: ZemavikConfig.from_dict(zemavik_fields(size)),
+            "rirusun": lambda size: RirusunConfig.from_dict(rirusun_fields(size))}
     record = {"metric": "prefill and decode, " + ", ".join(designs) + " at equal size", "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
               "data": "synthetic: random weights, uniform random token ids, caches filled by real prefill",
               "config": {"prefill_tokens": PREFILL_TOKENS, "decode_batch": batch, "decode_context": DESIGN_CONTEXT, "decode_steps": steps,
@@ -751,7 +777,7 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
     parser.add_argument("--workload", choices=["decode4b", "mixed8b", "sampled14b", "designs"], default="decode4b",
                         help="decode4b: the headline measurement (default); mixed8b, sampled14b: the serving workloads of the 8B and 14B shapes; "
-                             "designs: Vopepel, Fikerax and Zemavik beside Qwen3 at equal size, prefill and decode with the time of every kernel entry point")
+                             "designs: Vopepel, Fikerax, Zemavik and Rirusun beside Qwen3 at equal size, prefill and decode with the time of every kernel entry point")
     parser.add_argument("--design-sizes", default="2k,4k", help="with --workload designs: which of the sizes 2k, 4k")
     parser.add_argument("--designs", default=",".join(DESIGNS), help="with --workload designs: which of " + ", ".join(DESIGNS))
     parser.add_argument("--profile", choices=["decode", "prefill"],

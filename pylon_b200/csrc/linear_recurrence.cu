@@ -18,7 +18,9 @@
 //                            then it writes S and the last inputs back
 //
 // Everything but the operands of the products is float32: the sigmoids, softplus, decay and its logarithm, the state.
-// sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)), which keeps its digits when a is close to one.
+// sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)), which keeps its digits when a is close to one, and a * S as S + S * expm1(log a):
+// a channel that hardly decays has an a whose distance from one is a few units in its last place, and rounding a itself would change
+// that distance, the same way at every token, by a share that shows after a thousand tokens.
 #include "common.cuh"
 
 namespace pylon {
@@ -84,8 +86,7 @@ __global__ void linear_recurrence_scan_kernel(const T* __restrict__ proj, long l
     const float r = sigmoid_f(gates[t * 2 * channels + gate_column] + br);
     const float i = sigmoid_f(gates[t * 2 * channels + gate_column + part] + bi);
     const float log_a = -rate * r;
-    const float a = expf(log_a);
-    s = fmaf(a, s, sqrtf(-expm1f(2.f * log_a)) * i * u32[t * channels + c]);
+    s += fmaf(s, expm1f(log_a), sqrtf(-expm1f(2.f * log_a)) * i * u32[t * channels + c]);
     out[t * channels + c] = from_float<T>(s * gelu_tanh_f(to_float<T>(proj[t * ld + y_offset + c]) + by));
   }
   mine[c] = s;

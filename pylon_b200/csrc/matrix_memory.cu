@@ -60,8 +60,13 @@ __global__ void __launch_bounds__(MEMORY_WARPS * 32) matrix_memory_scan_kernel(
     const T* x = proj + (long long)t * ld;
     const float gi = cap * tanhf((gate_logits[(long long)t * 2 * heads + head] + bi) / cap);
     const float gf = log_sigmoid_f(cap * tanhf((gate_logits[(long long)t * 2 * heads + heads + head] + bf) / cap));
-    const float m_new = fmaxf(gf + m, gi);
-    const float keep = expf(gf + m - m_new), take = expf(gi - m_new);
+    // the sum f + m with what its rounding drops (two-sum): where it becomes the new maximum, the old content is kept times
+    // exp(-dropped), not times one - else every token would leave a factor of a few units in the last place of m behind
+    const float sum = gf + m;
+    const float part = sum - gf;
+    const float dropped = (gf - (sum - part)) + (m - part);
+    const float m_new = fmaxf(sum, gi);
+    const float keep = expf((sum - m_new) + dropped), take = expf(gi - m_new);
     m = m_new;
     float v[MEMORY_COLUMNS], o[MEMORY_COLUMNS];
 #pragma unroll
