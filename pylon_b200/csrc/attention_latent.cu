@@ -21,6 +21,12 @@
 #ifndef PYLON_LATENT_DIM
 #define PYLON_LATENT_DIM 576
 #endif
+// PYLON_LATENT_SPLIT_WEIGHTS 1: a softmax weight enters the second product as two bfloat16 numbers, the rounded weight and what the
+// rounding dropped (twice the products over the values), so that it counts with 16 of its 24 bits: for designs that ask for the
+// attention's weights in 32-bit.
+#ifndef PYLON_LATENT_SPLIT_WEIGHTS
+#define PYLON_LATENT_SPLIT_WEIGHTS 0
+#endif
 #ifndef PYLON_LATENT_VALUE_DIM
 #define PYLON_LATENT_VALUE_DIM 512
 #endif
@@ -109,6 +115,9 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
   // what the two warps of a row pair hand each other: their rows' maxima (and, at the end, sums), and their halves of a tile's weights
   __shared__ float pair_row[4][2][16];
   __shared__ __align__(16) __nv_bfloat16 pair_weights[4][16][LAT_BN + 8];
+#if PYLON_LATENT_SPLIT_WEIGHTS
+  __shared__ __align__(16) __nv_bfloat16 pair_dropped[4][16][LAT_BN + 8];   // what rounding the weights to bfloat16 dropped
+#endif
   auto pair_barrier = [](int pair) { asm volatile("bar.sync %0, 64;\n" ::"r"(pair + 1) : "memory"); };
   auto find_keys = [&](int key_tile, int which, int n) {
     const int j = key_tile * LAT_BN + n;
@@ -227,6 +236,12 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
       const int column = wn * 16 + n * 8 + (lane & 3) * 2;
       *reinterpret_cast<unsigned*>(&pair_weights[wm][lane >> 2][column]) = pack_bf16(p0, p1);
       *reinterpret_cast<unsigned*>(&pair_weights[wm][(lane >> 2) + 8][column]) = pack_bf16(p2, p3);
+#if PYLON_LATENT_SPLIT_WEIGHTS
+      *reinterpret_cast<unsigned*>(&pair_dropped[wm][lane >> 2][column]) =
+          pack_bf16(p0 - __bfloat162float(__float2bfloat16_rn(p0)), p1 - __bfloat162float(__float2bfloat16_rn(p1)));
+      *reinterpret_cast<unsigned*>(&pair_dropped[wm][(lane >> 2) + 8][column]) =
+          pack_bf16(p2 - __bfloat162float(__float2bfloat16_rn(p2)), p3 - __bfloat162float(__float2bfloat16_rn(p3)));
+#endif
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -252,6 +267,10 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
       for (int step = 0; step < 2; ++step) {
         unsigned a[4];
         ldmatrix_x4(a, p_from + step * 16);
+#if PYLON_LATENT_SPLIT_WEIGHTS
+        unsigned rest[4];
+        ldmatrix_x4(rest, &pair_dropped[wm][(lane & 7) + ((lane >> 3) & 1) * 8][(lane >> 4) * 8] + step * 16);
+#endif
 #pragma unroll
         for (int n = 0; n < LAT_NV_TILES; n += 2) {
           const int now = (step * (LAT_NV_TILES / 2) + (n >> 1)) & 1, next = now ^ 1;   // the fragments' buffers take turns across both steps
@@ -261,6 +280,10 @@ __global__ void __launch_bounds__(LAT_THREADS, 1) latent_attention_kernel(
             ldmatrix_x4_trans(b[next], v_from + 16 * LAT_PITCH);
           mma_bf16(o[n], a, b[now][0], b[now][1]);
           mma_bf16(o[n + 1], a, b[now][2], b[now][3]);
+#if PYLON_LATENT_SPLIT_WEIGHTS
+          mma_bf16(o[n], rest, b[now][0], b[now][1]);
+          mma_bf16(o[n + 1], rest, b[now][2], b[now][3]);
+#endif
         }
       }
     }

@@ -11,11 +11,13 @@
 //     out   = S * gate
 //
 // What a request carries from token to token is one float32 slot [C + (taps - 1) * C]: S, then the convolution's last taps - 1
-// inputs (x + b_x), oldest first.  Two kernels with the gates' product between them:
+// inputs (x + b_x), oldest first.  Three kernels with the gates' product behind the first:
 //
-//   linear_recurrence_conv   a thread per (token, channel): u in float32 and in the compute dtype (the product's operand)
-//   linear_recurrence_scan   a thread per (request row, channel) walks the row's tokens: gates, decay, state, out = S * gate;
-//                            then it writes S and the last inputs back
+//   linear_recurrence_conv    a thread per (token, channel): u in float32 and in the compute dtype (the product's operand)
+//   linear_recurrence_gates   a thread per (token, channel): everything of a token that does not need the state - a - 1, the term
+//                             sqrt(1 - a^2) * i * u and the gelu branch - so that the walk is left with two multiply-adds a token
+//   linear_recurrence_scan    a thread per (request row, channel) walks the row's tokens: S, out = S * gate; then it writes S and the
+//                             last inputs back
 //
 // Everything but the operands of the products is float32: the sigmoids, softplus, decay and its logarithm, the state.
 // sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)), which keeps its digits when a is close to one, and a * S as S + S * expm1(log a):
@@ -59,14 +61,36 @@ __global__ void linear_recurrence_conv_kernel(const T* __restrict__ proj, long l
   if (u16 != nullptr) u16[item] = from_float<T>(acc);
 }
 
-// gates float32 [T, blocks, 2 * part]: per block the r logits, then the i logits.  out [T, C] in T.
+// gates float32 [T, blocks, 2 * part]: per block the r logits, then the i logits.  decay_less_one, branch float32 [T, C] out; term: u in,
+// sqrt(1 - a^2) * i * u out, float32 [T, C] in place.
 template <typename T>
-__global__ void linear_recurrence_scan_kernel(const T* __restrict__ proj, long long ld, int y_offset, int x_offset, const float* __restrict__ bias_y,
-                                              const float* __restrict__ bias_x, const float* __restrict__ u32, const float* __restrict__ gates,
-                                              const float* __restrict__ bias_r, const float* __restrict__ bias_i, const float* __restrict__ lam,
-                                              float factor, int taps, float* __restrict__ state, long long state_floats,
-                                              const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int channels,
-                                              int part) {
+__global__ void linear_recurrence_gates_kernel(const T* __restrict__ proj, long long ld, int y_offset, const float* __restrict__ bias_y,
+                                               const float* __restrict__ gates, const float* __restrict__ bias_r, const float* __restrict__ bias_i,
+                                               const float* __restrict__ lam, float factor, const int* __restrict__ token_row,
+                                               float* __restrict__ term, float* __restrict__ decay_less_one, float* __restrict__ branch, int channels,
+                                               int part, long long total) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= total) return;
+  const long long t = item / channels;
+  const int c = (int)(item % channels);
+  if (token_row[t] < 0) return;   // a padding token: it belongs to no request
+  const long long gate_column = t * 2 * channels + (long long)(c / part) * 2 * part + c % part;
+  const float r = sigmoid_f(gates[gate_column] + bias_r[c]);
+  const float i = sigmoid_f(gates[gate_column + part] + bias_i[c]);
+  const float log_a = -factor * softplus_f(lam[c]) * r;
+  decay_less_one[item] = expm1f(log_a);
+  term[item] = sqrtf(-expm1f(2.f * log_a)) * i * term[item];
+  branch[item] = gelu_tanh_f(to_float<T>(proj[t * ld + y_offset + c]) + bias_y[c]);
+}
+
+// out [T, C] in T.
+template <typename T>
+__global__ void linear_recurrence_scan_kernel(const T* __restrict__ proj, long long ld, int x_offset, const float* __restrict__ bias_x,
+                                              const float* __restrict__ term, const float* __restrict__ decay_less_one,
+                                              const float* __restrict__ branch, int taps, float* __restrict__ state, long long state_floats,
+                                              const int* __restrict__ q_start, const int* __restrict__ slots, T* __restrict__ out, int channels) {
   grid_dependency_wait();
   allow_dependents();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -75,19 +99,12 @@ __global__ void linear_recurrence_scan_kernel(const T* __restrict__ proj, long l
   const int first = q_start[row], count = q_start[row + 1] - first;
   if (count <= 0) return;   // a row without tokens (a padded step): its state stays as it is
   float* mine = state + (long long)slots[row] * state_floats;
-  const int block = c / part, within = c % part;
-  const long long gate_column = (long long)block * 2 * part + within;
-  const float rate = factor * softplus_f(lam[c]);
-  const float br = bias_r[c], bi = bias_i[c], by = bias_y[c];
   float s = mine[c];
-#pragma unroll 4
+#pragma unroll 8
   for (int n = 0; n < count; ++n) {
-    const long long t = first + n;
-    const float r = sigmoid_f(gates[t * 2 * channels + gate_column] + br);
-    const float i = sigmoid_f(gates[t * 2 * channels + gate_column + part] + bi);
-    const float log_a = -rate * r;
-    s += fmaf(s, expm1f(log_a), sqrtf(-expm1f(2.f * log_a)) * i * u32[t * channels + c]);
-    out[t * channels + c] = from_float<T>(s * gelu_tanh_f(to_float<T>(proj[t * ld + y_offset + c]) + by));
+    const long long at = (long long)(first + n) * channels + c;
+    s += fmaf(s, decay_less_one[at], term[at]);
+    out[at] = from_float<T>(s * branch[at]);
   }
   mine[c] = s;
   // the last taps - 1 inputs, oldest first: from this step's tokens, and from the old ones where the step is shorter
@@ -124,22 +141,31 @@ extern "C" int pylon_linear_recurrence_conv(const void* proj, long long ld, int 
   PYLON_CHECK_LAUNCH("linear_recurrence_conv");
 }
 
+// term: float32 [T, C], u on entry and the recurrence's input term on return; decay_less_one, branch: float32 [T, C] scratch.
 extern "C" int pylon_linear_recurrence_scan(const void* proj, long long ld, int y_offset, int x_offset, const float* bias_y, const float* bias_x,
-                                            const float* u32, const float* gates, const float* bias_r, const float* bias_i, const float* lam, float factor,
-                                            int taps, float* state, long long state_floats, const int* q_start, const int* slots, void* out, int channels,
-                                            int blocks, int num_rows, int dtype, cudaStream_t stream) {
-  if (num_rows <= 0) return 0;
+                                            float* term, const float* gates, const float* bias_r, const float* bias_i, const float* lam, float factor,
+                                            int taps, float* state, long long state_floats, const int* token_row, const int* q_start, const int* slots,
+                                            float* decay_less_one, float* branch, void* out, int channels, int blocks, int num_rows, int num_tokens,
+                                            int dtype, cudaStream_t stream) {
+  if (num_rows <= 0 || num_tokens <= 0) return 0;
   if (channels < 1 || blocks < 1 || channels % blocks || taps < 1 || taps > RECURRENCE_MAX_TAPS || state_floats < (long long)channels * taps || num_rows > 65535)
     PYLON_REFUSE("linear_recurrence_scan: %d channels in %d blocks, %d taps, %d rows", channels, blocks, taps, num_rows);
   const int threads = 128;
   const dim3 grid((unsigned)((channels + threads - 1) / threads), (unsigned)num_rows);
   const int part = channels / blocks;
-  if (dtype == PYLON_DTYPE_F32)
-    launch_dependent(linear_recurrence_scan_kernel<float>, grid, dim3(threads), 0, stream, (const float*)proj, ld, y_offset, x_offset, bias_y, bias_x, u32, gates,
-                     bias_r, bias_i, lam, factor, taps, state, state_floats, q_start, slots, (float*)out, channels, part);
-  else if (dtype == PYLON_DTYPE_BF16)
-    launch_dependent(linear_recurrence_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)proj, ld, y_offset, x_offset, bias_y,
-                     bias_x, u32, gates, bias_r, bias_i, lam, factor, taps, state, state_floats, q_start, slots, (__nv_bfloat16*)out, channels, part);
-  else PYLON_REFUSE("linear_recurrence_scan: unknown dtype %d", dtype);
+  const long long total = (long long)num_tokens * channels;
+  const dim3 flat((unsigned)((total + 255) / 256));
+  if (dtype == PYLON_DTYPE_F32) {
+    launch_dependent(linear_recurrence_gates_kernel<float>, flat, dim3(256), 0, stream, (const float*)proj, ld, y_offset, bias_y, gates, bias_r, bias_i, lam,
+                     factor, token_row, term, decay_less_one, branch, channels, part, total);
+    launch_dependent(linear_recurrence_scan_kernel<float>, grid, dim3(threads), 0, stream, (const float*)proj, ld, x_offset, bias_x, (const float*)term,
+                     (const float*)decay_less_one, (const float*)branch, taps, state, state_floats, q_start, slots, (float*)out, channels);
+  } else if (dtype == PYLON_DTYPE_BF16) {
+    launch_dependent(linear_recurrence_gates_kernel<__nv_bfloat16>, flat, dim3(256), 0, stream, (const __nv_bfloat16*)proj, ld, y_offset, bias_y, gates, bias_r,
+                     bias_i, lam, factor, token_row, term, decay_less_one, branch, channels, part, total);
+    launch_dependent(linear_recurrence_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)proj, ld, x_offset, bias_x,
+                     (const float*)term, (const float*)decay_less_one, (const float*)branch, taps, state, state_floats, q_start, slots, (__nv_bfloat16*)out,
+                     channels);
+  } else PYLON_REFUSE("linear_recurrence_scan: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("linear_recurrence_scan");
 }

@@ -17,7 +17,9 @@
 // What a request carries from token to token is one float32 slot, per head [S (dim x vdim) | n (dim) | m].  The columns of S do not
 // see each other, so a block takes (request row, head, 32 columns): warp w of four owns eight neighbouring columns, lane l the rows
 // l, l + 32, ... of them (up to MEMORY_MAX_DIM rows), and a read-out is a sum over the lanes.  n and m are kept by every warp (the
-// same arithmetic in the same order); the first warp leaves their new values in a buffer beside the state, and a small kernel behind
+// same arithmetic in the same order from the gates' logarithms, which a kernel ahead of the walk forms for every token and head - the
+// walk is left with three exponentials a token); the eight read-outs of a warp are summed over its lanes together, each round of
+// exchanges halving what a lane holds (9 exchanges instead of 40); the first warp leaves their new values in a buffer beside the state, and a small kernel behind
 // the walk puts them into the slot (a block that starts late must still find the old ones there).  Everything is float32.
 #include "common.cuh"
 
@@ -29,10 +31,37 @@ constexpr int MEMORY_MAX_DIM = 256;      // rows of S: up to 8 a lane
 
 __device__ __forceinline__ float log_sigmoid_f(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+// In place on gate logits float32 [T, 2 heads] (the input gates', then the forget gates'): i = cap tanh((i + b_i) / cap),
+// f = logsigmoid(cap tanh((f + b_f) / cap)).
+__global__ void matrix_memory_gates_kernel(float* __restrict__ gates, const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap, int heads,
+                                           long long total) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= total) return;
+  const int column = (int)(item % (2 * heads));
+  const float x = gates[item];
+  gates[item] = column < heads ? cap * tanhf((x + bias_i[column]) / cap) : log_sigmoid_f(cap * tanhf((x + bias_f[column - heads]) / cap));
+}
+
+// Sums of eight values over the 32 lanes of a warp: the lane l with l % 4 == 0 returns the sum of value 4 (l / 16) + 2 (l / 8 % 2) + l / 4 % 2.
+__device__ __forceinline__ float warp_sum_of_eight(const float (&v)[8], int lane) {
+  float four[4], two[2];
+  const bool high16 = lane & 16, high8 = lane & 8, high4 = lane & 4;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) four[c] = (high16 ? v[c + 4] : v[c]) + __shfl_xor_sync(0xffffffffu, high16 ? v[c] : v[c + 4], 16);
+#pragma unroll
+  for (int c = 0; c < 2; ++c) two[c] = (high8 ? four[c + 2] : four[c]) + __shfl_xor_sync(0xffffffffu, high8 ? four[c] : four[c + 2], 8);
+  float one = (high4 ? two[1] : two[0]) + __shfl_xor_sync(0xffffffffu, high4 ? two[0] : two[1], 4);
+  one += __shfl_xor_sync(0xffffffffu, one, 2);
+  one += __shfl_xor_sync(0xffffffffu, one, 1);
+  return one;
+}
+
 template <typename T, int PER_LANE>
 __global__ void __launch_bounds__(MEMORY_WARPS * 32) matrix_memory_scan_kernel(
-    const T* __restrict__ proj, long long ld, const float* __restrict__ gate_logits, const float* __restrict__ bias_i, const float* __restrict__ bias_f,
-    float cap, float read_eps, float* __restrict__ state, long long state_floats, const int* __restrict__ q_start, const int* __restrict__ slots,
+    const T* __restrict__ proj, long long ld, const float* __restrict__ gate_logits,
+    float read_eps, float* __restrict__ state, long long state_floats, const int* __restrict__ q_start, const int* __restrict__ slots,
     float* __restrict__ read, float* __restrict__ fresh, int heads, int dim, int vdim) {
   grid_dependency_wait();
   allow_dependents();
@@ -52,14 +81,34 @@ __global__ void __launch_bounds__(MEMORY_WARPS * 32) matrix_memory_scan_kernel(
     for (int c = 0; c < MEMORY_COLUMNS; ++c) s[i][c] = (d < dim && j0 + c < vdim) ? mine[(long long)d * vdim + j0 + c] : 0.f;
   }
   float m = n_state[dim];
-  const float bi = bias_i[head], bf = bias_f[head];
   const float q_scale = rsqrtf((float)dim);
   const long long q_column = (long long)head * dim, k_column = (long long)heads * dim + q_column;
   const long long v_column = 2LL * heads * dim + (long long)head * vdim + j0;
-  for (int t = first; t < first + count; ++t) {
+  // what the next token brings is asked for while this token's arithmetic runs: the walk is a chain over tokens, and a load that
+  // starts only when its token's turn comes would put the memory's latency into every link
+  float k_next[PER_LANE], q_next[PER_LANE], v_next[MEMORY_COLUMNS], gi_next, gf_next;
+  auto fetch = [&](int t) {
     const T* x = proj + (long long)t * ld;
-    const float gi = cap * tanhf((gate_logits[(long long)t * 2 * heads + head] + bi) / cap);
-    const float gf = log_sigmoid_f(cap * tanhf((gate_logits[(long long)t * 2 * heads + heads + head] + bf) / cap));
+    gi_next = gate_logits[(long long)t * 2 * heads + head];            // the gates' logarithms, formed ahead of the walk
+    gf_next = gate_logits[(long long)t * 2 * heads + heads + head];
+#pragma unroll
+    for (int c = 0; c < MEMORY_COLUMNS; ++c) v_next[c] = j0 + c < vdim ? to_float<T>(x[v_column + c]) : 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int d = lane + 32 * i;
+      k_next[i] = d < dim ? to_float<T>(x[k_column + d]) : 0.f;
+      q_next[i] = d < dim ? to_float<T>(x[q_column + d]) * q_scale : 0.f;
+    }
+  };
+  fetch(first);
+  for (int t = first; t < first + count; ++t) {
+    float k_now[PER_LANE], q_now[PER_LANE], v[MEMORY_COLUMNS], o[MEMORY_COLUMNS];
+    const float gi = gi_next, gf = gf_next;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) { k_now[i] = k_next[i]; q_now[i] = q_next[i]; }
+#pragma unroll
+    for (int c = 0; c < MEMORY_COLUMNS; ++c) { v[c] = v_next[c]; o[c] = 0.f; }
+    if (t + 1 < first + count) fetch(t + 1);
     // the sum f + m with what its rounding drops (two-sum): where it becomes the new maximum, the old content is kept times
     // exp(-dropped), not times one - else every token would leave a factor of a few units in the last place of m behind
     const float sum = gf + m;
@@ -68,18 +117,10 @@ __global__ void __launch_bounds__(MEMORY_WARPS * 32) matrix_memory_scan_kernel(
     const float m_new = fmaxf(sum, gi);
     const float keep = expf((sum - m_new) + dropped), take = expf(gi - m_new);
     m = m_new;
-    float v[MEMORY_COLUMNS], o[MEMORY_COLUMNS];
-#pragma unroll
-    for (int c = 0; c < MEMORY_COLUMNS; ++c) {
-      v[c] = j0 + c < vdim ? to_float<T>(x[v_column + c]) : 0.f;
-      o[c] = 0.f;
-    }
     float nq = 0.f;
 #pragma unroll
     for (int i = 0; i < PER_LANE; ++i) {
-      const int d = lane + 32 * i;
-      const float k = d < dim ? to_float<T>(x[k_column + d]) * take : 0.f;
-      const float q = d < dim ? to_float<T>(x[q_column + d]) * q_scale : 0.f;
+      const float k = k_now[i] * take, q = q_now[i];
       n[i] = fmaf(keep, n[i], k);
       nq = fmaf(n[i], q, nq);
 #pragma unroll
@@ -90,13 +131,9 @@ __global__ void __launch_bounds__(MEMORY_WARPS * 32) matrix_memory_scan_kernel(
     }
     nq = warp_sum(nq);
     const float below = fmaxf(fabsf(nq), expf(-m)) + read_eps;
-    float result = 0.f;
-#pragma unroll
-    for (int c = 0; c < MEMORY_COLUMNS; ++c) {
-      const float sum = warp_sum(o[c]);
-      if (lane == c) result = sum;
-    }
-    if (lane < MEMORY_COLUMNS && j0 + lane < vdim) read[(long long)t * heads * vdim + (long long)head * vdim + j0 + lane] = result / below;
+    const float result = warp_sum_of_eight(o, lane);
+    const int column = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+    if ((lane & 3) == 0 && j0 + column < vdim) read[(long long)t * heads * vdim + (long long)head * vdim + j0 + column] = result / below;
   }
 #pragma unroll
   for (int i = 0; i < PER_LANE; ++i) {
@@ -146,12 +183,12 @@ __global__ void matrix_memory_out_kernel(const float* __restrict__ read, const T
 
 using namespace pylon;
 
-// proj [T, ld] in dtype, columns [q | k | v | g]; gate_logits float32 [T, 2 heads]; state float32 [slots, state_floats]; read float32
+// proj [T, ld] in dtype, columns [q | k | v | g]; gate_logits float32 [T, 2 heads], replaced by the gates' logarithms; state float32 [slots, state_floats]; read float32
 // [T, heads * vdim] out; fresh float32 [num_rows, heads, dim + 1]: scratch.
-extern "C" int pylon_matrix_memory_scan(const void* proj, long long ld, const float* gate_logits, const float* bias_i, const float* bias_f, float cap,
+extern "C" int pylon_matrix_memory_scan(const void* proj, long long ld, float* gate_logits, const float* bias_i, const float* bias_f, float cap,
                                         float read_eps, float* state, long long state_floats, const int* q_start, const int* slots, float* read, float* fresh,
-                                        int heads, int dim, int vdim, int num_rows, int dtype, cudaStream_t stream) {
-  if (num_rows <= 0) return 0;
+                                        int heads, int dim, int vdim, int num_rows, int num_tokens, int dtype, cudaStream_t stream) {
+  if (num_rows <= 0 || num_tokens <= 0) return 0;
   if (heads < 1 || dim < 1 || dim > MEMORY_MAX_DIM || vdim < 1 || !(cap > 0.f) || num_rows > 65535 || heads > 65535 ||
       state_floats < (long long)heads * ((long long)dim * vdim + dim + 1))
     PYLON_REFUSE("matrix_memory_scan: %d heads of %d x %d (at most %d rows), cap %f, %d request rows", heads, dim, vdim, MEMORY_MAX_DIM, cap, num_rows);
@@ -159,8 +196,10 @@ extern "C" int pylon_matrix_memory_scan(const void* proj, long long ld, const fl
   const dim3 grid((unsigned)((vdim + per_block - 1) / per_block), (unsigned)heads, (unsigned)num_rows);
   const dim3 block(MEMORY_WARPS * 32);
   const int per_lane = (dim + 31) / 32;
+  const long long gate_items = (long long)num_tokens * 2 * heads;
+  launch_dependent(matrix_memory_gates_kernel, dim3((unsigned)((gate_items + 255) / 256)), dim3(256), 0, stream, gate_logits, bias_i, bias_f, cap, heads, gate_items);
 #define PYLON_MEMORY(T, P)                                                                                                                          \
-  launch_dependent(matrix_memory_scan_kernel<T, P>, grid, block, 0, stream, (const T*)proj, ld, gate_logits, bias_i, bias_f, cap, read_eps, state, \
+  launch_dependent(matrix_memory_scan_kernel<T, P>, grid, block, 0, stream, (const T*)proj, ld, (const float*)gate_logits, read_eps, state,          \
                    state_floats, q_start, slots, read, fresh, heads, dim, vdim)
 #define PYLON_MEMORY_T(T)                                                                          \
   do {                                                                                             \

@@ -201,11 +201,12 @@ _SIGNATURES = {
         "pylon_linear_recurrence_conv": [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "pylon_linear_recurrence_scan": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
-                                         c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                                         c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                         c_int, c_void_p],
     },
     "matrix_memory.cu": {
         "pylon_matrix_memory_scan": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "pylon_matrix_memory_out": [c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "combine.cu": {
@@ -274,6 +275,12 @@ _SIGNATURES = {
         "pylon_paged_attention_simple": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
                                          c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    },
+    "attention_window.cu": {
+        "pylon_window_attention": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+        "pylon_window_attention_max_group": [],
+        "pylon_window_attention_scratch_floats": [c_int, c_int, c_int],
     },
     "attention_mma.cu": {
         "pylon_paged_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -862,12 +869,18 @@ def paged_attention(
     values_in_keys: Optional[int] = None,
     keep_first: int = 0,
     distance_bias: Optional[torch.Tensor] = None,
+    split_weights: bool = False,
 ) -> torch.Tensor:
     """Causal attention of every token of a step over its request's pages.
 
+    ``split_weights`` (latent rows on the tensor cores): a softmax weight enters the weighted sum as two bfloat16 numbers, the rounded
+    weight and what the rounding dropped, so that it counts with 16 bits instead of 8, at twice the products over the values.
+
     ``keep_first`` n: a window never hides the keys at positions below n (a token sees ``j <= p`` with ``p - j < window`` or
     ``j < n``).  ``distance_bias``: float32 ``[rows, nq]``; the scaled score of the key ``p - j`` positions back gets
-    ``distance_bias[min(p - j, rows - 1), h]`` added.  Both run on the plain kernel.
+    ``distance_bias[min(p - j, rows - 1), h]`` added.  These, sinks and values of another width than the keys run in bfloat16 on a
+    tensor-core kernel of their own (``csrc/attention_window.cu``, built per pair of sizes on first use: keys of a multiple of 16 and
+    values of a multiple of 8 up to 256, at most 8 query heads to a KV head), else on the plain kernel.
 
     ``sinks``: float32 ``[nq]``; the softmax's denominator of head h also holds ``exp(sinks[h])``, a key without a
     value whose score is taken as it stands.  ``values_in_keys`` n (with ``v_pages=None``): the values are the first n
@@ -911,7 +924,7 @@ def paged_attention(
         _need(v_pages is None and k_pages.dim() == 4 and k_pages.is_contiguous() and 1 <= values_in_keys <= k_pages.shape[3],
               "paged_attention: values inside the key rows are their first columns, and there are no value pages then")
         return _latent_attention(q, k_pages, int(values_in_keys), positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale,
-                                 sinks, out, force_simple, num_splits)
+                                 sinks, out, force_simple, num_splits, split_weights)
     _need(k_pages.dim() == 4 and v_pages.dim() == 4 and k_pages.shape[:3] == v_pages.shape[:3] and k_pages.is_contiguous() and v_pages.is_contiguous()
           and k_pages.dtype == v_pages.dtype, "paged_attention: pages must be contiguous [P, nkv, page_size, d] and [P, nkv, page_size, value width]")
     num_pages, nkv, page_size, d = k_pages.shape
@@ -978,6 +991,20 @@ def paged_attention(
             scale, rows, tokens,
             int(max_q), splits, blocks, int(use_tcgen05), int(bool(rows_alike)), _ptr(attention_error_word(q.device)), _stream()))
         return out
+    if ((plain_only or sinks is not None) and q.dtype == torch.bfloat16 and not force_simple and chunk is None and softcap is None and d % 16 == 0 and d <= 256 and dv % 8 == 0 and dv <= 256
+            and nq // nkv <= 8 and q.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0):
+        library = _library("attention_window.cu", {"PYLON_HEAD_DIM": d, "PYLON_VALUE_DIM": dv})
+        splits = window_attention_splits(rows, nkv, max_q, max_kv, window, keep_first, _multiprocessors(q.device)) if num_splits is None else int(num_splits)
+        scratch = None
+        if splits > 1:
+            scratch = torch.empty((library.pylon_window_attention_scratch_floats(splits, tokens, nq),), dtype=torch.float32, device=q.device)
+        _check(library, library.pylon_window_attention(
+            _ptr(q), q.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.shape[1], page_size,
+            num_pages, nq, nkv, int(window or 0), int(keep_first), scale, _ptr(distance_bias), 0 if distance_bias is None else distance_bias.shape[0],
+            _ptr(sinks), rows, int(max_q), splits, _ptr(scratch), _ptr(token_row), tokens, _ptr(attention_error_word(q.device)), _stream()))
+        if splits > 1:
+            launches[0] += 1   # the parts' sum is a kernel of its own
+        return out
     _need(d <= 2048 and dv <= 512, f"paged_attention: head sizes {d} / {dv}: at most 2048 / 512")
     library = _library("attention_simple.cu")
     _check(library, library.pylon_paged_attention_simple(
@@ -985,6 +1012,17 @@ def paged_attention(
         block_table.shape[1], page_size, num_pages, nq, nkv, d, dv, int(window or 0), int(chunk or 0), float(softcap or 0.0), scale,
         _ptr(sinks), 0, 0, tokens, _dtype_code(q.dtype), int(keep_first), _ptr(distance_bias), 0 if distance_bias is None else distance_bias.shape[0], _stream()))
     return out
+
+
+def window_attention_splits(rows: int, nkv: int, max_q: int, max_kv: int, window: Optional[int], keep_first: int, sms: int) -> int:
+    """Over how many blocks the kernel for windows with kept first keys deals out the key tiles of 16 tokens of one KV head: one for steps
+    with enough blocks to fill the device (prompt portions); for a few decoded tokens as many as give every SM two blocks, each with
+    at least two key tiles of 32."""
+    blocks = rows * nkv * -(-max_q // 16)
+    key_tiles = -(-min(max_kv, (window or max_kv) + keep_first + 16) // 32)
+    if blocks >= sms or key_tiles < 4:
+        return 1
+    return int(max(1, min(key_tiles // 2, 2 * sms // blocks, 32)))
 
 
 def latent_attention_splits(rows: int, nq: int, max_q: int, max_kv: int, window: Optional[int], sms: int) -> int:
@@ -998,7 +1036,8 @@ def latent_attention_splits(rows: int, nq: int, max_q: int, max_kv: int, window:
     return int(max(1, min(key_tiles // 2, 2 * sms // tiles, 64)))
 
 
-def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale, sinks, out, force_simple, num_splits):
+def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block_table, nq, max_q, max_kv, window, scale, sinks, out, force_simple, num_splits,
+                      split_weights=False):
     """Attention of ``nq`` heads over one shared row per token: keys are the whole rows ``[d]``, values their first ``dv`` columns.
     bfloat16 rows of a multiple of 16 numbers (up to 832) with values of a multiple of 32 (up to 512) run on the tensor cores
     (``csrc/attention_latent.cu``, built per pair of sizes on first use); float32 and other sizes take the plain kernel."""
@@ -1018,7 +1057,10 @@ def _latent_attention(q, pages, dv, positions, token_row, q_start, kv_len, block
     _need(q_start.dtype == torch.int32 and q_start.is_contiguous() and q_start.shape[0] >= rows + 1, "paged_attention: q_start must be int32 [rows + 1]")
     _need(kv_len.dtype == torch.int32 and kv_len.is_contiguous() and kv_len.shape[0] >= rows, "paged_attention: kv_len must be int32 [rows]")
     if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 832 and dv % 32 == 0 and not force_simple and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
-        library = _library("attention_latent.cu", {"PYLON_LATENT_DIM": d, "PYLON_LATENT_VALUE_DIM": dv})
+        defines = {"PYLON_LATENT_DIM": d, "PYLON_LATENT_VALUE_DIM": dv}
+        if split_weights:   # the weights with 16 bits in the second product (a library of its own)
+            defines["PYLON_LATENT_SPLIT_WEIGHTS"] = 1
+        library = _library("attention_latent.cu", defines)
         splits = latent_attention_splits(rows, nq, max_q, max_kv, window, _multiprocessors(q.device)) if num_splits is None else int(num_splits)
         scratch = None
         if splits > 1:
@@ -1340,9 +1382,12 @@ def linear_recurrence(proj: torch.Tensor, bias: torch.Tensor, conv_weight: torch
     operand = (u32 if u16 is None else u16).view(tokens, blocks, channels // blocks)
     gates = linear_heads(operand, w_gates, out_dtype=torch.float32)   # [T, blocks, 2 C / blocks], float32 sums whatever the operands
     out = torch.empty((tokens, channels), dtype=proj.dtype, device=device)
+    scratch = torch.empty((2, tokens, channels), dtype=torch.float32, device=device)   # a - 1 and the gelu branch of every token
     _check(library, library.pylon_linear_recurrence_scan(
         _ptr(proj), proj.stride(0), 0, channels, _ptr(bias), _ptr(bias[channels:]), _ptr(u32), _ptr(gates), _ptr(gate_bias), _ptr(gate_bias[1]), _ptr(lam),
-        float(factor), taps, _ptr(state), state.shape[1], _ptr(q_start), _ptr(slots), _ptr(out), channels, blocks, num_rows, code, _stream()))
+        float(factor), taps, _ptr(state), state.shape[1], _ptr(token_row), _ptr(q_start), _ptr(slots), _ptr(scratch[0]), _ptr(scratch[1]), _ptr(out),
+        channels, blocks, num_rows, tokens, code, _stream()))
+    launches[0] += 1   # two kernels: what a token needs besides the state, then the walk
     return out
 
 
@@ -1352,7 +1397,7 @@ def matrix_memory(proj: torch.Tensor, gate_logits: torch.Tensor, gate_bias: torc
     """A matrix of memory per head with exponential gates over the tokens of a step (``csrc/matrix_memory.cu`` has the equations).
 
     ``proj [T, 2 heads dim + 2 heads vdim]``: the projection of the layer's input, columns ``[q | k | v | g]``; ``gate_logits`` float32
-    ``[T, 2 heads]``: the input gates', then the forget gates'; ``gate_bias`` float32 ``[2, heads]`` to match; ``norm_weight`` float32
+    ``[T, 2 heads]``: the input gates', then the forget gates' (replaced by the gates' logarithms); ``gate_bias`` float32 ``[2, heads]`` to match; ``norm_weight`` float32
     ``[heads * vdim]``; ``state`` float32 ``[slots, heads * (dim * vdim + dim + 1)]``: per request and head the matrix, the normaliser
     and the running maximum, read at ``state[slots[row]]`` and advanced in place by the row's tokens.  Returns ``[T, heads * vdim]`` in
     ``proj``'s dtype: the read-out, normed per head, times the weight and ``sigmoid(g)``, ready for the output projection."""
@@ -1373,8 +1418,8 @@ def matrix_memory(proj: torch.Tensor, gate_logits: torch.Tensor, gate_bias: torc
     library = _library("matrix_memory.cu")
     _check(library, library.pylon_matrix_memory_scan(
         _ptr(proj), proj.stride(0), _ptr(gate_logits), _ptr(gate_bias), _ptr(gate_bias[1]), float(cap), float(read_eps), _ptr(state), state.shape[1],
-        _ptr(q_start), _ptr(slots), _ptr(read), _ptr(fresh), heads, dim, vdim, num_rows, code, _stream()))
-    launches[0] += 1   # the walk is followed by the small kernel that puts the normaliser and the maximum into the slots
+        _ptr(q_start), _ptr(slots), _ptr(read), _ptr(fresh), heads, dim, vdim, num_rows, tokens, code, _stream()))
+    launches[0] += 2   # three kernels: the gates' logarithms, the walk, the normaliser and the maximum into the slots
     out = torch.empty((tokens, heads * vdim), dtype=proj.dtype, device=device)
     _check(library, library.pylon_matrix_memory_out(_ptr(read), _ptr(proj), proj.stride(0), 2 * heads * dim + heads * vdim, _ptr(norm_weight), float(norm_eps),
                                                     _ptr(out), heads, vdim, tokens, code, _stream()))

@@ -50,7 +50,7 @@ def _mixer(config: RirusunConfig, layer: RirusunLayer, index: int, positions: in
                                      "layout": "halves"})
     return PartSpec("latent_attention", {
         "width": config.width, "n_heads": heads, "head_dim": dim, "rot_dim": rot_dim, "value_dim": vdim, "q_rank": None, "kv_rank": kv_rank,
-        "norm_eps": config.norm_eps, "scale": scale, "position": rotation, "names": {"q": "q"},
+        "norm_eps": config.norm_eps, "scale": scale, "position": rotation, "names": {"q": "q"}, "split_weights": True,
     })
 
 

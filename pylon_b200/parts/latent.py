@@ -34,7 +34,7 @@ class LatentAttention(Mixer):
 
     def __init__(self, width: int, n_heads: int, head_dim: int, rot_dim: int, value_dim: int, q_rank: Optional[int], kv_rank: int, norm_eps: float,
                  scale: float, position: Optional[PartSpec] = None, window: Optional[int] = None, sink: bool = False,
-                 names: Optional[Mapping[str, str]] = None) -> None:
+                 names: Optional[Mapping[str, str]] = None, split_weights: bool = False) -> None:
         self.width, self.n_heads, self.head_dim, self.rot_dim = int(width), int(n_heads), int(head_dim), int(rot_dim)
         self.value_dim, self.q_rank, self.kv_rank = int(value_dim), (None if q_rank is None else int(q_rank)), int(kv_rank)
         if min(self.n_heads, self.head_dim, self.value_dim, self.q_rank or 1, self.kv_rank) < 1 or self.rot_dim < 0:
@@ -42,6 +42,7 @@ class LatentAttention(Mixer):
         self.norm_eps, self.scale = float(norm_eps), float(scale)
         self.window = None if window is None else int(window)
         self.has_sink = bool(sink)
+        self.split_weights = bool(split_weights)   # the tensor-core kernel takes the softmax weights with 16 bits instead of 8 (twice the products over the values)
         self.position = POSITION_ENCODINGS.build(position) if position is not None and self.rot_dim else None
         if self.position is not None and not hasattr(self.position, "tables"):
             raise ValueError("latent attention rotates its shared key part by tables of cos and sin")
@@ -111,7 +112,7 @@ class LatentAttention(Mixer):
         context = ops.paged_attention(
             query.view(tokens, self.n_heads * self.row), cache.k_pages, None, step.positions, step.token_row, step.q_start, step.kv_len,
             cache.block_table, self.n_heads, step.max_q, step.max_kv, window=self.window, scale=self.scale, row_tokens=step.row_tokens,
-            sinks=self.sink, values_in_keys=self.kv_rank,
+            sinks=self.sink, values_in_keys=self.kv_rank, split_weights=self.split_weights,
         )
         values = ops.linear_heads(context.view(tokens, self.n_heads, self.kv_rank), self.w_uv)
         return ops.linear_for_residual(values.view(tokens, self.n_heads * self.value_dim), self.w_o)
