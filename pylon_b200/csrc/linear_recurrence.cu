@@ -18,6 +18,11 @@
 //                             sqrt(1 - a^2) * i * u and the gelu branch - so that the walk is left with two multiply-adds a token
 //   linear_recurrence_scan    a thread per (request row, channel) walks the row's tokens: S, out = S * gate; then it writes S and the
 //                             last inputs back
+// Long rows (a prompt) are walked in segments side by side instead: the recurrence is linear in S, so a segment walked from S = 0
+// gives its own share L and, as the sum of its log a, the factor on what entered it: S_out = S_in + S_in expm1(sum log a) + L (again
+// without rounding a product of decays close to one).  `segment_local` (a thread per row, segment and channel), `segment_carry` (a
+// thread per row and channel: the segments' entering states in order, the slot's new state and kept inputs), `segment_walk` (every
+// segment again from its entering state, writing out).
 //
 // Everything but the operands of the products is float32: the sigmoids, softplus, decay and its logarithm, the state.
 // sqrt(1 - a^2) is formed as sqrt(-expm1(2 log a)), which keeps its digits when a is close to one, and a * S as S + S * expm1(log a):
@@ -118,6 +123,85 @@ __global__ void linear_recurrence_scan_kernel(const T* __restrict__ proj, long l
   for (int k = 0; k < taps - 1; ++k) history[(long long)k * channels + c] = keep[k];
 }
 
+// local, log_sum float32 [rows, segments, C] out.
+__global__ void linear_recurrence_segment_local_kernel(const float* __restrict__ term, const float* __restrict__ decay_less_one,
+                                                       const int* __restrict__ q_start, float* __restrict__ local, float* __restrict__ log_sum,
+                                                       int channels, int segments) {
+  grid_dependency_wait();
+  allow_dependents();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int segment = blockIdx.y, row = blockIdx.z;
+  if (c >= channels) return;
+  const int first = q_start[row], count = q_start[row + 1] - first;
+  if (count <= 0) return;
+  const int each = (count + segments - 1) / segments;
+  const int begin = segment * each, end = begin + each < count ? begin + each : count;
+  float s = 0.f, logs = 0.f;
+#pragma unroll 8
+  for (int n = begin; n < end; ++n) {
+    const long long at = (long long)(first + n) * channels + c;
+    const float less = decay_less_one[at];
+    s += fmaf(s, less, term[at]);
+    logs += log1pf(less);
+  }
+  const long long where = ((long long)row * segments + segment) * channels + c;
+  local[where] = s;
+  log_sum[where] = logs;
+}
+
+// carry float32 [rows, segments, C] out: the state that enters each segment.
+template <typename T>
+__global__ void linear_recurrence_segment_carry_kernel(const T* __restrict__ proj, long long ld, int x_offset, const float* __restrict__ bias_x,
+                                                       const float* __restrict__ local, const float* __restrict__ log_sum, float* __restrict__ carry,
+                                                       int taps, float* __restrict__ state, long long state_floats, const int* __restrict__ q_start,
+                                                       const int* __restrict__ slots, int channels, int segments) {
+  grid_dependency_wait();
+  allow_dependents();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int row = blockIdx.y;
+  if (c >= channels) return;
+  const int first = q_start[row], count = q_start[row + 1] - first;
+  if (count <= 0) return;
+  float* mine = state + (long long)slots[row] * state_floats;
+  float s = mine[c];
+  for (int segment = 0; segment < segments; ++segment) {
+    const long long where = ((long long)row * segments + segment) * channels + c;
+    carry[where] = s;
+    s += fmaf(s, expm1f(log_sum[where]), local[where]);
+  }
+  mine[c] = s;
+  float keep[RECURRENCE_MAX_TAPS];
+  float* history = mine + channels;
+  const float bx = bias_x[c];
+  for (int k = 0; k < taps - 1; ++k) {
+    const int n = count - (taps - 1) + k;
+    keep[k] = n >= 0 ? to_float<T>(proj[(long long)(first + n) * ld + x_offset + c]) + bx : history[(long long)(taps - 1 + n) * channels + c];
+  }
+  for (int k = 0; k < taps - 1; ++k) history[(long long)k * channels + c] = keep[k];
+}
+
+template <typename T>
+__global__ void linear_recurrence_segment_walk_kernel(const float* __restrict__ term, const float* __restrict__ decay_less_one,
+                                                      const float* __restrict__ branch, const float* __restrict__ carry,
+                                                      const int* __restrict__ q_start, T* __restrict__ out, int channels, int segments) {
+  grid_dependency_wait();
+  allow_dependents();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int segment = blockIdx.y, row = blockIdx.z;
+  if (c >= channels) return;
+  const int first = q_start[row], count = q_start[row + 1] - first;
+  if (count <= 0) return;
+  const int each = (count + segments - 1) / segments;
+  const int begin = segment * each, end = begin + each < count ? begin + each : count;
+  float s = carry[((long long)row * segments + segment) * channels + c];
+#pragma unroll 8
+  for (int n = begin; n < end; ++n) {
+    const long long at = (long long)(first + n) * channels + c;
+    s += fmaf(s, decay_less_one[at], term[at]);
+    out[at] = from_float<T>(s * branch[at]);
+  }
+}
+
 }  // namespace pylon
 
 using namespace pylon;
@@ -142,27 +226,50 @@ extern "C" int pylon_linear_recurrence_conv(const void* proj, long long ld, int 
 }
 
 // term: float32 [T, C], u on entry and the recurrence's input term on return; decay_less_one, branch: float32 [T, C] scratch.
+// segments > 1: every row is walked in so many segments side by side, with segment_scratch float32 [3, num_rows, segments, C].
 extern "C" int pylon_linear_recurrence_scan(const void* proj, long long ld, int y_offset, int x_offset, const float* bias_y, const float* bias_x,
                                             float* term, const float* gates, const float* bias_r, const float* bias_i, const float* lam, float factor,
                                             int taps, float* state, long long state_floats, const int* token_row, const int* q_start, const int* slots,
                                             float* decay_less_one, float* branch, void* out, int channels, int blocks, int num_rows, int num_tokens,
-                                            int dtype, cudaStream_t stream) {
+                                            int segments, float* segment_scratch, int dtype, cudaStream_t stream) {
   if (num_rows <= 0 || num_tokens <= 0) return 0;
   if (channels < 1 || blocks < 1 || channels % blocks || taps < 1 || taps > RECURRENCE_MAX_TAPS || state_floats < (long long)channels * taps || num_rows > 65535)
     PYLON_REFUSE("linear_recurrence_scan: %d channels in %d blocks, %d taps, %d rows", channels, blocks, taps, num_rows);
+  if (segments < 1 || segments > 1024 || (segments > 1 && !segment_scratch)) PYLON_REFUSE("linear_recurrence_scan: %d segments", segments);
   const int threads = 128;
   const dim3 grid((unsigned)((channels + threads - 1) / threads), (unsigned)num_rows);
+  const dim3 by_segment((unsigned)((channels + threads - 1) / threads), (unsigned)segments, (unsigned)num_rows);
+  const long long one = (long long)num_rows * segments * channels;
+  float* local = segment_scratch;
+  float* log_sum = segment_scratch ? segment_scratch + one : nullptr;
+  float* carry = segment_scratch ? segment_scratch + 2 * one : nullptr;
   const int part = channels / blocks;
   const long long total = (long long)num_tokens * channels;
   const dim3 flat((unsigned)((total + 255) / 256));
   if (dtype == PYLON_DTYPE_F32) {
     launch_dependent(linear_recurrence_gates_kernel<float>, flat, dim3(256), 0, stream, (const float*)proj, ld, y_offset, bias_y, gates, bias_r, bias_i, lam,
                      factor, token_row, term, decay_less_one, branch, channels, part, total);
+    if (segments > 1) {
+      launch_dependent(linear_recurrence_segment_local_kernel, by_segment, dim3(threads), 0, stream, (const float*)term, (const float*)decay_less_one, q_start,
+                       local, log_sum, channels, segments);
+      launch_dependent(linear_recurrence_segment_carry_kernel<float>, grid, dim3(threads), 0, stream, (const float*)proj, ld, x_offset, bias_x,
+                       (const float*)local, (const float*)log_sum, carry, taps, state, state_floats, q_start, slots, channels, segments);
+      launch_dependent(linear_recurrence_segment_walk_kernel<float>, by_segment, dim3(threads), 0, stream, (const float*)term, (const float*)decay_less_one,
+                       (const float*)branch, (const float*)carry, q_start, (float*)out, channels, segments);
+    } else
     launch_dependent(linear_recurrence_scan_kernel<float>, grid, dim3(threads), 0, stream, (const float*)proj, ld, x_offset, bias_x, (const float*)term,
                      (const float*)decay_less_one, (const float*)branch, taps, state, state_floats, q_start, slots, (float*)out, channels);
   } else if (dtype == PYLON_DTYPE_BF16) {
     launch_dependent(linear_recurrence_gates_kernel<__nv_bfloat16>, flat, dim3(256), 0, stream, (const __nv_bfloat16*)proj, ld, y_offset, bias_y, gates, bias_r,
                      bias_i, lam, factor, token_row, term, decay_less_one, branch, channels, part, total);
+    if (segments > 1) {
+      launch_dependent(linear_recurrence_segment_local_kernel, by_segment, dim3(threads), 0, stream, (const float*)term, (const float*)decay_less_one, q_start,
+                       local, log_sum, channels, segments);
+      launch_dependent(linear_recurrence_segment_carry_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)proj, ld, x_offset, bias_x,
+                       (const float*)local, (const float*)log_sum, carry, taps, state, state_floats, q_start, slots, channels, segments);
+      launch_dependent(linear_recurrence_segment_walk_kernel<__nv_bfloat16>, by_segment, dim3(threads), 0, stream, (const float*)term,
+                       (const float*)decay_less_one, (const float*)branch, (const float*)carry, q_start, (__nv_bfloat16*)out, channels, segments);
+    } else
     launch_dependent(linear_recurrence_scan_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)proj, ld, x_offset, bias_x,
                      (const float*)term, (const float*)decay_less_one, (const float*)branch, taps, state, state_floats, q_start, slots, (__nv_bfloat16*)out,
                      channels);

@@ -202,7 +202,7 @@ _SIGNATURES = {
                                          c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "pylon_linear_recurrence_scan": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                          c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                         c_int, c_void_p],
+                                         c_int, c_void_p, c_int, c_void_p],
     },
     "matrix_memory.cu": {
         "pylon_matrix_memory_scan": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
@@ -1350,14 +1350,15 @@ def _rows_meta(what: str, tokens: int, num_rows: int, **tensors: torch.Tensor) -
 
 def linear_recurrence(proj: torch.Tensor, bias: torch.Tensor, conv_weight: torch.Tensor, conv_bias: torch.Tensor, w_gates: torch.Tensor,
                       gate_bias: torch.Tensor, lam: torch.Tensor, factor: float, state: torch.Tensor, token_row: torch.Tensor, q_start: torch.Tensor,
-                      slots: torch.Tensor, num_rows: int) -> torch.Tensor:
+                      slots: torch.Tensor, num_rows: int, max_q: Optional[int] = None) -> torch.Tensor:
     """A gated linear recurrence per channel over the tokens of a step (``csrc/linear_recurrence.cu`` has the equations).
 
     ``proj [T, 2 C]``: the projection of the layer's input, columns ``[y | x]``, and ``bias`` float32 ``[2 C]`` to match; ``conv_weight``
     float32 ``[C, taps]`` (the last tap weighs the current token) and ``conv_bias`` float32 ``[C]``; ``w_gates [blocks, 2 C / blocks, C / blocks]``
     in ``proj``'s dtype: per block of channels the rows of the recurrence gate's map, then those of the input gate's; ``gate_bias`` float32
     ``[2, C]`` (recurrence gate, input gate); ``lam`` float32 ``[C]``; ``state`` float32 ``[slots, C + (taps - 1) * C]``: per request the
-    recurrence's state and the convolution's last inputs, read at ``state[slots[row]]`` and advanced in place by the row's tokens.  Returns
+    recurrence's state and the convolution's last inputs, read at ``state[slots[row]]`` and advanced in place by the row's tokens.
+    ``max_q``: the most tokens a row brings (an upper bound is fine): rows of 256 tokens and more are walked in segments side by side.  Returns
     ``[T, C]`` in ``proj``'s dtype: state times ``gelu_tanh(y)``, ready for the output projection."""
     _need_cuda(proj, bias, conv_weight, conv_bias, w_gates, gate_bias, lam, state, token_row, q_start, slots)
     tokens, channels = proj.shape[0], proj.shape[1] // 2
@@ -1383,11 +1384,14 @@ def linear_recurrence(proj: torch.Tensor, bias: torch.Tensor, conv_weight: torch
     gates = linear_heads(operand, w_gates, out_dtype=torch.float32)   # [T, blocks, 2 C / blocks], float32 sums whatever the operands
     out = torch.empty((tokens, channels), dtype=proj.dtype, device=device)
     scratch = torch.empty((2, tokens, channels), dtype=torch.float32, device=device)   # a - 1 and the gelu branch of every token
+    longest = tokens if max_q is None else min(tokens, int(max_q))
+    segments = 1 if longest < 256 else min(64, longest // 64)   # by the step's size alone: the same launches whatever the rows hold
+    segment_scratch = torch.empty((3, num_rows, segments, channels), dtype=torch.float32, device=device) if segments > 1 else None
     _check(library, library.pylon_linear_recurrence_scan(
         _ptr(proj), proj.stride(0), 0, channels, _ptr(bias), _ptr(bias[channels:]), _ptr(u32), _ptr(gates), _ptr(gate_bias), _ptr(gate_bias[1]), _ptr(lam),
         float(factor), taps, _ptr(state), state.shape[1], _ptr(token_row), _ptr(q_start), _ptr(slots), _ptr(scratch[0]), _ptr(scratch[1]), _ptr(out),
-        channels, blocks, num_rows, tokens, code, _stream()))
-    launches[0] += 1   # two kernels: what a token needs besides the state, then the walk
+        channels, blocks, num_rows, tokens, segments, _ptr(segment_scratch), code, _stream()))
+    launches[0] += 1 if segments == 1 else 3   # what a token needs besides the state, then the walk (in segments: three kernels)
     return out
 
 

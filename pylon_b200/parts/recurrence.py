@@ -68,5 +68,5 @@ class GatedLinearRecurrence(Mixer):
     def forward(self, h: torch.Tensor, step: StepView, cache: LayerCache) -> torch.Tensor:
         proj = ops.linear(h, self.w_in)
         out = ops.linear_recurrence(proj, self.bias, self.conv_weight, self.conv_bias, self.w_gates, self.gate_bias, self.lam, self.decay_factor,
-                                    cache.state, step.token_row, step.q_start, step.slots, step.num_rows)
+                                    cache.state, step.token_row, step.q_start, step.slots, step.num_rows, step.max_q)
         return ops.linear_for_residual(out, self.w_o)
