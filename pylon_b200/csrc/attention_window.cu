@@ -7,9 +7,11 @@
 // denominator of head h also holds exp(sinks[h]), a key without a value.  Query head h reads KV head h / (nq / nkv).
 //
 // A block takes 16 neighbouring tokens of one request and one KV head; its warps are the query heads of that KV head (at most 8),
-// so a tile of 32 keys and their values is fetched from the pages once for the whole group: the keys row by row, the values
-// transposed, so that both products read their B operands as 32-bit words without bank conflicts.  Tiles: the kept first keys,
-// then from the first key the block's first token sees to its last token; what a token does not see inside a tile is masked.
+// so a tile of 32 keys and their values is fetched from the pages once for the whole group, by cp.async into one of two stages while
+// the tile before is worked on (where the tile's keys lie in the pages is looked up a tile further ahead); rows padded so that the
+// first product's 32-bit fragment loads and the second's ldmatrix (transposing: the values lie row by row as they came) meet no bank
+// twice.  Tiles: the kept first keys, then from the first key the block's first token sees to its last token; what a token does not
+// see inside a tile is masked.
 // Softmax online in float32.  The weights enter the second product as two bfloat16 numbers each, the rounded weight and what
 // the rounding dropped, so that they count with 16 bits of their 24: the sum of weights and the weighted sum agree to float32's
 // own rounding of the products.  Built per (key size, value size); both are multiples of 16 and 8 up to 256.
@@ -34,7 +36,7 @@ constexpr int WINDOW_TOKENS = 16;   // tokens of a block
 constexpr int WINDOW_KEYS = 32;     // keys of a tile
 constexpr int WINDOW_MAX_GROUP = 8; // query heads per KV head: the warps of a block
 constexpr int K_LD = D + 8;         // 16-bit elements between the rows of the key tile: 32-bit fragment loads fall into 32 banks
-constexpr int VT_LD = WINDOW_KEYS + 8;
+constexpr int V_LD = DV + 8;         // likewise between the rows of the value tile: the eight 16-byte rows of an ldmatrix fall into different banks
 
 struct WindowParams {
   const __nv_bfloat16* q;
@@ -65,9 +67,16 @@ __device__ __forceinline__ unsigned pack_bf16(float low, float high) {
   return *reinterpret_cast<const unsigned*>(&pair);
 }
 
+__device__ __forceinline__ void window_copy_or_zeros(void* shared, const void* global, bool real) {
+  const unsigned target = (unsigned)__cvta_generic_to_shared(shared);
+  const int bytes = real ? 16 : 0;   // what is not copied is written as zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(target), "l"(global), "r"(bytes) : "memory");
+}
+
 __global__ void __launch_bounds__(WINDOW_MAX_GROUP * 32) window_attention_kernel(WindowParams p) {
-  __shared__ __align__(16) __nv_bfloat16 k_tile[WINDOW_KEYS * K_LD];
-  __shared__ __align__(16) __nv_bfloat16 vt_tile[DV * VT_LD];
+  extern __shared__ __align__(16) unsigned char window_stages[];   // two stages of [keys K_LD | values V_LD] rows
+  __shared__ long long key_row[2][WINDOW_KEYS];   // the cache row (page, KV head, slot) of every key of a tile, -1: none
+  constexpr int STAGE_ELEMENTS = WINDOW_KEYS * (K_LD + V_LD);
   grid_dependency_wait();
   allow_dependents();
   const int row = blockIdx.z, kv_head = blockIdx.y;
@@ -81,6 +90,7 @@ __global__ void __launch_bounds__(WINDOW_MAX_GROUP * 32) window_attention_kernel
   const int group = p.nq / p.nkv;
   const int head = kv_head * group + warp;
   const int* table = p.block_table + (size_t)row * p.table_width;
+  const float* bias_of_head = p.bias ? p.bias + head : nullptr;
 
   // the queries of the warp's head: 16 tokens x D as A fragments (rows group_id and group_id + 8), zeros for tokens the row does not have
   unsigned qa[D / 16][4];
@@ -109,44 +119,68 @@ __global__ void __launch_bounds__(WINDOW_MAX_GROUP * 32) window_attention_kernel
   const int lo_first = p.window > 0 ? (p0 - p.window + 1 > 0 ? p0 - p.window + 1 : 0) : 0;   // the first key of the window of the block's first token
   const int kept = p.keep_first < lo_first ? p.keep_first : lo_first;                        // the keys before it that stay visible: [0, kept)
   const int kept_end = (kept + WINDOW_KEYS - 1) / WINDOW_KEYS * WINDOW_KEYS;
-  int tile_start = kept > 0 ? 0 : lo_first / WINDOW_KEYS * WINDOW_KEYS;
-  for (int turn = 0; tile_start <= p_last; ++turn) {
-    if (turn % p.splits != split) {   // another split's tile (the same for every thread of the block)
+  // the block's tiles in order: every `splits`-th tile of the kept keys' tiles and then the window's; beyond p_last: none left
+  auto after = [&](int tile_start) {
+    for (int turn = 0; turn < p.splits && tile_start <= p_last; ++turn) {
       tile_start += WINDOW_KEYS;
-      if (tile_start == kept_end && kept > 0) {
+      if (tile_start == kept_end && kept > 0) {   // behind the kept keys' tiles: on to the window's first tile, if that lies further on
         const int window_start = lo_first / WINDOW_KEYS * WINDOW_KEYS;
         if (window_start > tile_start) tile_start = window_start;
       }
-      continue;
     }
-    __syncthreads();   // the tile before is used up
-    for (int x = threadIdx.x; x < WINDOW_KEYS * (D / 8); x += blockDim.x) {
-      const int key = x / (D / 8), piece = x % (D / 8);
-      const int j = tile_start + key;
-      uint4 value = make_uint4(0, 0, 0, 0);
+    return tile_start;
+  };
+  auto look_up = [&](int stage, int tile_start) {   // where every key of the tile lies: looked up once, a tile ahead of its copies
+    if (threadIdx.x < WINDOW_KEYS) {
+      const int j = tile_start + threadIdx.x;
+      long long where = -1;
       if (j <= p_last && (j >= lo_first || j < kept)) {
         const int page = table[j / p.page_size];
-        if (page >= 0 && page < p.num_pages)
-          value = *reinterpret_cast<const uint4*>(p.k_pages + (((size_t)page * p.nkv + kv_head) * p.page_size + j % p.page_size) * D + piece * 8);
+        if (page >= 0 && page < p.num_pages) where = ((long long)page * p.nkv + kv_head) * p.page_size + j % p.page_size;
         else if (p.error) atomicExch(p.error, PYLON_ERROR_BAD_PAGE);   // a key that is seen has a page
       }
-      *reinterpret_cast<uint4*>(k_tile + key * K_LD + piece * 8) = value;
+      key_row[stage][threadIdx.x] = where;
     }
-    for (int x = threadIdx.x; x < WINDOW_KEYS * (DV / 8); x += blockDim.x) {
-      const int key = x % WINDOW_KEYS, piece = x / WINDOW_KEYS;   // neighbouring threads take neighbouring keys: their transposed stores lie side by side
-      const int j = tile_start + key;
-      uint4 value = make_uint4(0, 0, 0, 0);
-      if (j <= p_last && (j >= lo_first || j < kept)) {
-        const int page = table[j / p.page_size];
-        if (page >= 0 && page < p.num_pages)
-          value = *reinterpret_cast<const uint4*>(p.v_pages + (((size_t)page * p.nkv + kv_head) * p.page_size + j % p.page_size) * DV + piece * 8);
+  };
+  auto issue = [&](int stage, int tile_start) {   // the tile's keys and values on their way into the stage (an empty group behind the last tile)
+    if (tile_start <= p_last) {
+      __nv_bfloat16* k_tile = reinterpret_cast<__nv_bfloat16*>(window_stages) + (size_t)stage * STAGE_ELEMENTS;
+      __nv_bfloat16* v_tile = k_tile + WINDOW_KEYS * K_LD;
+      for (int x = threadIdx.x; x < WINDOW_KEYS * (D / 8); x += blockDim.x) {
+        const int key = x / (D / 8), piece = x % (D / 8);
+        const long long where = key_row[stage][key];
+        window_copy_or_zeros(k_tile + key * K_LD + piece * 8, where >= 0 ? p.k_pages + where * D + piece * 8 : p.k_pages, where >= 0);
       }
-      const __nv_bfloat16* elements = reinterpret_cast<const __nv_bfloat16*>(&value);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) vt_tile[(piece * 8 + e) * VT_LD + key] = elements[e];
+      for (int x = threadIdx.x; x < WINDOW_KEYS * (DV / 8); x += blockDim.x) {
+        const int key = x / (DV / 8), piece = x % (DV / 8);
+        const long long where = key_row[stage][key];
+        window_copy_or_zeros(v_tile + key * V_LD + piece * 8, where >= 0 ? p.v_pages + where * DV + piece * 8 : p.v_pages, where >= 0);
+      }
     }
-    __syncthreads();
-    if (warp < group) {
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+  int tile_start = kept > 0 ? 0 : lo_first / WINDOW_KEYS * WINDOW_KEYS;
+  for (int turn = 0; turn < split && tile_start <= p_last; ++turn) {   // this split's first tile
+    tile_start += WINDOW_KEYS;
+    if (tile_start == kept_end && kept > 0) {
+      const int window_start = lo_first / WINDOW_KEYS * WINDOW_KEYS;
+      if (window_start > tile_start) tile_start = window_start;
+    }
+  }
+  int next_start = after(tile_start);
+  look_up(0, tile_start);
+  look_up(1, next_start);
+  __syncthreads();
+  issue(0, tile_start);
+  for (int stage = 0; tile_start <= p_last; stage ^= 1) {
+    issue(stage ^ 1, next_start);                       // the next tile's copies run while this tile is worked on
+    const int third_start = after(next_start);
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");   // this tile has arrived (for this thread's copies)
+    __syncthreads();                                          // ... for everyone's; and this stage's look-ups are used up
+    look_up(stage, third_start);                              // read when the tile after the next is issued, two barriers on
+    const __nv_bfloat16* k_tile = reinterpret_cast<const __nv_bfloat16*>(window_stages) + (size_t)stage * STAGE_ELEMENTS;
+    const __nv_bfloat16* v_tile = k_tile + WINDOW_KEYS * K_LD;
+    {
       float s[WINDOW_KEYS / 8][4];
 #pragma unroll
       for (int nt = 0; nt < WINDOW_KEYS / 8; ++nt) {
@@ -169,7 +203,7 @@ __global__ void __launch_bounds__(WINDOW_MAX_GROUP * 32) window_attention_kernel
           float score = -INFINITY;
           if (seen) {
             score = s[nt][e] * p.scale;
-            if (p.bias) score += p.bias[(size_t)(pos - j < p.bias_rows ? pos - j : p.bias_rows - 1) * p.nq + head];
+            if (p.bias) score += bias_of_head[(pos - j < p.bias_rows ? pos - j : p.bias_rows - 1) * p.nq];
           }
           s[nt][e] = score;
           tile_top[r] = fmaxf(tile_top[r], score);
@@ -180,7 +214,7 @@ __global__ void __launch_bounds__(WINDOW_MAX_GROUP * 32) window_attention_kernel
         tile_top[r] = fmaxf(tile_top[r], __shfl_xor_sync(0xffffffffu, tile_top[r], 1));
         tile_top[r] = fmaxf(tile_top[r], __shfl_xor_sync(0xffffffffu, tile_top[r], 2));
         const float new_top = fmaxf(top[r], tile_top[r]);
-        rescale[r] = (top[r] == -INFINITY || new_top == -INFINITY) ? (new_top == -INFINITY ? 1.f : 0.f) : expf(top[r] - new_top);
+        rescale[r] = (top[r] == -INFINITY || new_top == -INFINITY) ? (new_top == -INFINITY ? 1.f : 0.f) : __expf(top[r] - new_top);
         top[r] = new_top;
         sum[r] *= rescale[r];
       }
@@ -191,7 +225,7 @@ __global__ void __launch_bounds__(WINDOW_MAX_GROUP * 32) window_attention_kernel
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int r = e >> 1;
-          w[e] = s[nt][e] == -INFINITY ? 0.f : expf(s[nt][e] - top[r]);
+          w[e] = s[nt][e] == -INFINITY ? 0.f : __expf(s[nt][e] - top[r]);   // the hardware's exponential: a relative 2^-21, below what the weights carry on
           sum[r] += w[e];
           rest[e] = w[e] - __bfloat162float(__float2bfloat16_rn(w[e]));
         }
@@ -200,26 +234,28 @@ __global__ void __launch_bounds__(WINDOW_MAX_GROUP * 32) window_attention_kernel
         dropped[nt >> 1][(nt & 1) * 2] = pack_bf16(rest[0], rest[1]);
         dropped[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(rest[2], rest[3]);
       }
+      // the values lie row by row as they came; ldmatrix with .trans hands each lane its two keys of one column: rows 16 ks + (lane % 16)
+      const unsigned v_from = (unsigned)__cvta_generic_to_shared(v_tile + (lane & 15) * V_LD);
 #pragma unroll
       for (int nt = 0; nt < DV / 8; ++nt) {
         o[nt][0] *= rescale[0]; o[nt][1] *= rescale[0];
         o[nt][2] *= rescale[1]; o[nt][3] *= rescale[1];
 #pragma unroll
         for (int ks = 0; ks < WINDOW_KEYS / 16; ++ks) {
-          const __nv_bfloat16* from = vt_tile + (8 * nt + group_id) * VT_LD + 16 * ks + 2 * quad;
-          const unsigned b0 = *reinterpret_cast<const unsigned*>(from), b1 = *reinterpret_cast<const unsigned*>(from + 8);
+          unsigned b0, b1;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0, %1}, [%2];\n"
+                       : "=r"(b0), "=r"(b1)
+                       : "r"(v_from + (unsigned)((16 * ks * V_LD + 8 * nt) * sizeof(__nv_bfloat16))));
           mma_bf16(o[nt], weights[ks], b0, b1);
           mma_bf16(o[nt], dropped[ks], b0, b1);
         }
       }
     }
-    tile_start += WINDOW_KEYS;
-    if (tile_start == kept_end && kept > 0) {   // behind the kept keys' tiles: on to the window's first tile, if that lies further on
-      const int window_start = lo_first / WINDOW_KEYS * WINDOW_KEYS;
-      if (window_start > tile_start) tile_start = window_start;
-    }
+    __syncthreads();   // the stage is free for the tile after the next
+    tile_start = next_start;
+    next_start = third_start;
   }
-  if (warp >= group) return;
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
@@ -313,7 +349,15 @@ extern "C" int pylon_window_attention(const void* q, long long q_stride, const v
   p.scale = scale; p.bias = bias; p.sinks = sinks; p.error = error; p.splits = splits; p.total_tokens = total_tokens; p.scratch = scratch;
   const int group = nq / nkv;
   const dim3 grid((unsigned)((max_q + WINDOW_TOKENS - 1) / WINDOW_TOKENS * splits), (unsigned)nkv, (unsigned)num_rows);
-  launch_dependent(window_attention_kernel, grid, dim3(group * 32), 0, stream, p);
+  const size_t stages = 2 * (size_t)WINDOW_KEYS * (K_LD + V_LD) * sizeof(__nv_bfloat16);
+  if (stages > 48 * 1024) {
+    static bool raised[MAX_DEVICES] = {};   // function attributes belong to a device
+    if (!raised[current_device_slot()]) {
+      cudaFuncSetAttribute(window_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)stages);
+      raised[current_device_slot()] = true;
+    }
+  }
+  launch_dependent(window_attention_kernel, grid, dim3(group * 32), stages, stream, p);
   if (splits > 1) {
     const long long items = (long long)total_tokens * nq;
     launch_dependent(window_attention_combine_kernel, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, stream, (const float*)scratch, (__nv_bfloat16*)out,
