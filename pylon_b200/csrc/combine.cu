@@ -28,6 +28,22 @@ __device__ __forceinline__ float unit_activation(float x, int kind) {
   return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));   // gelu, tanh form
 }
 
+// The same for bfloat16 in whole 16-byte pieces: a thread takes eight neighbouring elements.
+__global__ void activation_vec_kernel(uint4* __restrict__ x, long long pieces, int kind) {
+  grid_dependency_wait();
+  allow_dependents();
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= pieces) return;
+  uint4 eight = x[item];
+  __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&eight);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(pairs[i]);
+    pairs[i] = __floats2bfloat162_rn(unit_activation(v.x, kind), unit_activation(v.y, kind));
+  }
+  x[item] = eight;
+}
+
 // In place: x <- act(x), element by element.
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ x, long long total, int kind) {
@@ -344,6 +360,8 @@ extern "C" int pylon_activation(void* x, long long total, int kind, int dtype, c
   if (kind < 0 || kind > 3) PYLON_REFUSE("activation: kind %d", kind);
   const dim3 grid((unsigned)((total + 255) / 256));
   if (dtype == PYLON_DTYPE_F32) launch_dependent(activation_kernel<float>, grid, dim3(256), 0, stream, (float*)x, total, kind);
+  else if (dtype == PYLON_DTYPE_BF16 && total % 8 == 0 && (uintptr_t)x % 16 == 0)
+    launch_dependent(activation_vec_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream, (uint4*)x, total / 8, kind);
   else if (dtype == PYLON_DTYPE_BF16) launch_dependent(activation_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)x, total, kind);
   else PYLON_REFUSE("activation: unknown dtype %d", dtype);
   PYLON_CHECK_LAUNCH("activation");
