@@ -725,7 +725,7 @@ class RirusunAttention:
     dim: int
     vdim: int
     scale: float
-    bias_max: int
+    bias_max: float
     window: Optional[int] = None
     keep_first: int = 0
     bias_rows: Optional[int] = None    # rows of the bias table: the checkpoint's tensor shape gives them (a configuration written for random weights names them)
@@ -743,7 +743,10 @@ class RirusunAttention:
             keep = int(mask.get("keep_first") or 0)
             if keep < 0:
                 raise ConfigError(f"{where}: mask.keep_first must not be negative")
-        return cls(heads, kv_heads, _positive_int(data, "dim"), _positive_int(data, "vdim"), _number(data, "scale"), _positive_int(data, "bias_max"),
+        far = _number(data, "bias_max")    # a distance; whole in every model seen, but nothing in the table's rule needs that
+        if not far > 0:
+            raise ConfigError(f"{where}: bias_max must be positive")
+        return cls(heads, kv_heads, _positive_int(data, "dim"), _positive_int(data, "vdim"), _number(data, "scale"), int(far) if far == int(far) else far,
                    window, keep, None if data.get("bias_rows") is None else _positive_int(data, "bias_rows"))
 
     def to_dict(self) -> dict[str, Any]:
